@@ -1,0 +1,229 @@
+// torch_op.cpp — the drop-in torch-op boundary: `fwd` and `get_scheduler_metadata` with the schemas of
+// the reference (kernels/fa4_blackwell.cu:10187-10205; the vLLM `_vllm_fa3_C` surface), registered under
+// the namespace given by -DFA3_LIB_NAME (default `_vllm_fa3_C`, as kernels/fa3_hopper.cu:34-36).
+// This file only unpacks tensors into the plain-pointer structs of include/fa_b200.h and calls the C ABI.
+// PyTorch is used for device memory (outputs, scratch) and the current stream — nothing is computed here.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/all.h>
+#include <torch/library.h>
+
+#include <cstdlib>
+#include <optional>
+#include <vector>
+
+#include "../../include/fa_b200.h"
+
+#ifndef FA3_LIB_NAME
+#define FA3_LIB_NAME _vllm_fa3_C
+#endif
+
+namespace {
+
+int dtype_code(at::ScalarType t) {
+  if (t == at::kBFloat16) return FA_DT_BF16;
+  if (t == at::kHalf) return FA_DT_FP16;
+  if (t == at::kFloat8_e4m3fn) return FA_DT_FP8_E4M3;
+  return -1;
+}
+
+const int32_t* i32(const std::optional<at::Tensor>& t, const char* name) {
+  if (!t.has_value()) return nullptr;
+  TORCH_CHECK(t->scalar_type() == at::kInt && t->is_contiguous() && t->is_cuda(), name,
+              " must be a contiguous int32 CUDA tensor");
+  return t->data_ptr<int32_t>();
+}
+
+bool env_flag(const char* name) {
+  const char* v = std::getenv(name);
+  return v && v[0] && v[0] != '0';
+}
+
+void check_rc(int rc, const char* what) {
+  if (rc == FA_OK) return;
+  TORCH_CHECK(false, "fa_b200: ", what, ": ", fa_b200_strerror(rc),
+              rc == FA_ERR_LAUNCH ? " — " : "", rc == FA_ERR_LAUNCH ? fa_b200_last_cuda_error() : "");
+}
+
+// Mirrors mha_fwd (kernels/fa4_blackwell.cu:10081-10173): same arguments, same return
+// {out, softmax_lse, empty, empty}; unsupported configurations raise with "unsupported" in the text.
+std::vector<at::Tensor> mha_fwd(
+    at::Tensor q, at::Tensor k, at::Tensor v,
+    std::optional<at::Tensor> k_new, std::optional<at::Tensor> v_new, std::optional<at::Tensor> q_v,
+    std::optional<at::Tensor> out_,
+    std::optional<at::Tensor> cu_seqlens_q, std::optional<at::Tensor> cu_seqlens_k,
+    std::optional<at::Tensor> cu_seqlens_k_new,
+    std::optional<at::Tensor> seqused_q, std::optional<at::Tensor> seqused_k,
+    std::optional<int64_t> max_seqlen_q, std::optional<int64_t> max_seqlen_k,
+    std::optional<at::Tensor> page_table, std::optional<at::Tensor> kv_batch_idx,
+    std::optional<at::Tensor> leftpad_k,
+    std::optional<at::Tensor> rotary_cos, std::optional<at::Tensor> rotary_sin,
+    std::optional<at::Tensor> seqlens_rotary,
+    std::optional<at::Tensor> q_descale, std::optional<at::Tensor> k_descale, std::optional<at::Tensor> v_descale,
+    double softmax_scale, bool is_causal, int64_t window_size_left, int64_t window_size_right,
+    double softcap, bool is_rotary_interleaved,
+    std::optional<at::Tensor> scheduler_metadata, int64_t num_splits, std::optional<bool> pack_gqa,
+    int64_t sm_margin,
+    std::optional<at::Tensor> s_aux, int64_t cp_world_size, int64_t cp_rank,
+    std::optional<at::Tensor> cp_tot_seqused_k) {
+  TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "fa_b200: q, k, v must be CUDA tensors");
+  const at::cuda::OptionalCUDAGuard guard(q.device());
+  TORCH_CHECK(q.dim() == 3, "fa_b200: q must be (total_q, hq, hd)");
+  const bool paged = page_table.has_value();
+  TORCH_CHECK(k.dim() == (paged ? 4 : 3) && v.dim() == k.dim(), "fa_b200: k/v rank does not match paged=", paged);
+  TORCH_CHECK(!k_new.has_value() && !v_new.has_value() && !q_v.has_value() && !rotary_cos.has_value() &&
+                  !rotary_sin.has_value() && !kv_batch_idx.has_value() && !seqused_q.has_value() &&
+                  !cu_seqlens_k_new.has_value() && cp_world_size <= 1,
+              "fa_b200: unsupported config (k_new/v_new/q_v/rotary/kv_batch_idx/seqused_q/context-parallel)");
+  TORCH_CHECK(cu_seqlens_q.has_value(), "fa_b200: unsupported config (cu_seqlens_q is required)");
+  TORCH_CHECK(q.stride(2) == 1 && k.stride(-1) == 1 && v.stride(-1) == 1, "fa_b200: last dim must be contiguous");
+
+  FaFwdParams p{};
+  p.total_q = (int)q.size(0); p.hq = (int)q.size(1); p.hd = (int)q.size(2);
+  p.hkv = paged ? (int)k.size(2) : (int)k.size(1);
+  p.hdv = paged ? (int)v.size(3) : (int)v.size(2);
+  p.q_dtype = dtype_code(q.scalar_type());
+  p.kv_dtype = dtype_code(k.scalar_type());
+  TORCH_CHECK(p.q_dtype >= 0 && p.kv_dtype >= 0 && k.scalar_type() == v.scalar_type(),
+              "fa_b200: unsupported config (dtype q=", q.scalar_type(), " k=", k.scalar_type(), ")");
+  const auto out_type = q.scalar_type() == at::kFloat8_e4m3fn ? at::kBFloat16 : q.scalar_type();
+  p.out_dtype = dtype_code(out_type);
+
+  at::Tensor out = out_.has_value() ? *out_ : at::empty({p.total_q, p.hq, p.hdv}, q.options().dtype(out_type));
+  TORCH_CHECK(out.scalar_type() == out_type && out.dim() == 3 && out.size(0) == p.total_q && out.size(1) == p.hq &&
+                  out.size(2) == p.hdv && out.stride(2) == 1,
+              "fa_b200: out has the wrong shape, dtype or layout");
+  at::Tensor lse = at::empty({p.hq, p.total_q}, q.options().dtype(at::kFloat));
+
+  p.q = q.data_ptr(); p.k = k.data_ptr(); p.v = v.data_ptr(); p.out = out.data_ptr();
+  p.lse = lse.data_ptr<float>();
+  p.q_row_stride = q.stride(0); p.q_head_stride = q.stride(1);
+  p.o_row_stride = out.stride(0); p.o_head_stride = out.stride(1);
+  if (paged) {
+    p.k_page_stride = k.stride(0); p.k_row_stride = k.stride(1); p.k_head_stride = k.stride(2);
+    p.v_page_stride = v.stride(0); p.v_row_stride = v.stride(1); p.v_head_stride = v.stride(2);
+    p.page_size = (int)k.size(1); p.num_pages = (int)k.size(0);
+    p.page_table = i32(page_table, "page_table");
+    TORCH_CHECK(page_table->dim() == 2, "fa_b200: page_table must be (batch, max_pages)");
+    p.page_table_stride = (int)page_table->stride(0);
+    TORCH_CHECK(seqused_k.has_value(), "fa_b200: unsupported config (paged KV needs seqused_k)");
+  } else {
+    p.k_row_stride = k.stride(0); p.k_head_stride = k.stride(1);
+    p.v_row_stride = v.stride(0); p.v_head_stride = v.stride(1);
+    p.total_k = (int)k.size(0);
+    TORCH_CHECK(cu_seqlens_k.has_value(), "fa_b200: unsupported config (non-paged KV needs cu_seqlens_k)");
+  }
+  p.cu_seqlens_q = i32(cu_seqlens_q, "cu_seqlens_q");
+  p.cu_seqlens_k = i32(cu_seqlens_k, "cu_seqlens_k");
+  p.seqused_k = i32(seqused_k, "seqused_k");
+  p.leftpad_k = i32(leftpad_k, "leftpad_k");
+  p.batch = (int)cu_seqlens_q->numel() - 1;
+  TORCH_CHECK(max_seqlen_q.has_value() && max_seqlen_k.has_value(),
+              "fa_b200: max_seqlen_q and max_seqlen_k are required");
+  p.max_seqlen_q = (int)*max_seqlen_q; p.max_seqlen_k = (int)*max_seqlen_k;
+
+  // fp8 descales: (batch, hkv) float tables or one-element tensors, materialised as (batch, hkv) fp32
+  at::Tensor qd, kd, vd;
+  auto descale = [&](const std::optional<at::Tensor>& d, at::Tensor& keep, const char* name) -> const float* {
+    if (!d.has_value()) return nullptr;
+    TORCH_CHECK(d->is_cuda(), name, " must be a CUDA tensor");
+    at::Tensor f = d->to(at::kFloat);
+    if (f.numel() == 1) f = f.reshape({1, 1});
+    TORCH_CHECK(f.dim() == 2 && (f.size(0) == p.batch || f.size(0) == 1) && (f.size(1) == p.hkv || f.size(1) == 1),
+                name, " must be (batch, hkv) or a single element");
+    keep = f.expand({p.batch, p.hkv}).contiguous();
+    return keep.data_ptr<float>();
+  };
+  p.q_descale = descale(q_descale, qd, "q_descale");
+  p.k_descale = descale(k_descale, kd, "k_descale");
+  p.v_descale = descale(v_descale, vd, "v_descale");
+  p.descale_batch_stride = p.hkv; p.descale_head_stride = 1;
+
+  at::Tensor s_aux_f;
+  if (s_aux.has_value()) {
+    s_aux_f = s_aux->to(at::kFloat).contiguous();
+    TORCH_CHECK(s_aux_f.numel() == p.hq, "fa_b200: s_aux must have one logit per q head");
+    p.s_aux = s_aux_f.data_ptr<float>();
+  }
+  p.scheduler_metadata = i32(scheduler_metadata, "scheduler_metadata");
+  if (scheduler_metadata.has_value() && scheduler_metadata->numel() < 16) p.scheduler_metadata = nullptr;
+
+  p.softmax_scale = (float)softmax_scale; p.softcap = (float)softcap;
+  p.is_causal = is_causal ? 1 : 0;
+  p.window_left = (int)window_size_left; p.window_right = (int)window_size_right;
+  p.num_splits = (int)num_splits; p.sm_margin = (int)sm_margin;
+  p.route = FA_ROUTE_AUTO;
+  if (const char* r = std::getenv("FA_B200_ROUTE")) p.route = std::atoi(r);
+
+  const size_t ws_bytes = fa_b200_fwd_workspace_bytes(&p);
+  at::Tensor ws = at::empty({(int64_t)ws_bytes}, q.options().dtype(at::kByte));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  const int rc = fa_b200_fwd(&p, ws.data_ptr(), ws_bytes, (fa_stream_t)stream.stream());
+  if (rc == FA_ERR_UNSUPPORTED) {
+    TORCH_CHECK(false, "fa_b200: unsupported config (hd=", p.hd, " hdv=", p.hdv, " paged=", paged,
+                " page_size=", p.page_size, " q dtype=", q.scalar_type(), " kv dtype=", k.scalar_type(), ")");
+  }
+  check_rc(rc, "fwd");
+  if (env_flag("FA_B200_CHECK_STATUS")) {
+    uint32_t detail = 0;
+    const int st = fa_b200_check_status(ws.data_ptr(), (fa_stream_t)stream.stream(), &detail);
+    TORCH_CHECK(st == FA_OK, "fa_b200: ", fa_b200_strerror(st), " (detail=", detail, ")");
+  }
+  at::Tensor empty = at::empty({0}, q.options().dtype(at::kFloat));
+  return {out, lse, empty, empty};
+}
+
+// Mirrors mha_fwd_get_scheduler_metadata (kernels/fa4_blackwell.cu:10175-10183): same arguments; returns an
+// int32 tensor that `fwd` accepts back through `scheduler_metadata`.
+at::Tensor mha_fwd_get_scheduler_metadata(
+    int64_t batch_size, int64_t max_seqlen_q, int64_t max_seqlen_k, int64_t num_heads, int64_t num_heads_k,
+    int64_t headdim, int64_t headdim_v, at::ScalarType qkv_dtype, at::Tensor seqused_k,
+    std::optional<at::Tensor> cu_seqlens_q, std::optional<at::Tensor> cu_seqlens_k,
+    std::optional<at::Tensor> cu_seqlens_k_new, std::optional<at::Tensor> seqused_q,
+    std::optional<at::Tensor> leftpad_k, std::optional<int64_t> page_size, int64_t max_seqlen_k_new,
+    bool is_causal, int64_t window_size_left, int64_t window_size_right, bool has_softcap, int64_t num_splits,
+    std::optional<bool> pack_gqa, int64_t sm_margin) {
+  TORCH_CHECK(seqused_k.is_cuda(), "fa_b200: seqused_k must be a CUDA tensor");
+  const at::cuda::OptionalCUDAGuard guard(seqused_k.device());
+  FaSchedParams sp{};
+  std::optional<at::Tensor> su(seqused_k);
+  sp.seqused_k = i32(su, "seqused_k");
+  sp.cu_seqlens_q = i32(cu_seqlens_q, "cu_seqlens_q");
+  sp.cu_seqlens_k = i32(cu_seqlens_k, "cu_seqlens_k");
+  sp.leftpad_k = i32(leftpad_k, "leftpad_k");
+  sp.batch = (int)batch_size; sp.max_seqlen_q = (int)max_seqlen_q; sp.max_seqlen_k = (int)max_seqlen_k;
+  sp.hq = (int)num_heads; sp.hkv = (int)num_heads_k; sp.hd = (int)headdim; sp.hdv = (int)headdim_v;
+  sp.qkv_dtype = dtype_code(qkv_dtype);
+  TORCH_CHECK(sp.qkv_dtype >= 0, "fa_b200: unsupported config (qkv_dtype)");
+  sp.page_size = page_size.has_value() ? (int)*page_size : 0;
+  sp.is_causal = is_causal; sp.window_left = (int)window_size_left; sp.window_right = (int)window_size_right;
+  sp.has_softcap = has_softcap; sp.num_splits = (int)num_splits; sp.sm_margin = (int)sm_margin;
+  const int len = fa_b200_scheduler_metadata_len(&sp);
+  at::Tensor md = at::empty({len}, seqused_k.options().dtype(at::kInt));
+  auto stream = at::cuda::getCurrentCUDAStream();
+  check_rc(fa_b200_get_scheduler_metadata(&sp, md.data_ptr<int32_t>(), (fa_stream_t)stream.stream()),
+           "get_scheduler_metadata");
+  return md;
+}
+
+}  // namespace
+
+TORCH_LIBRARY(FA3_LIB_NAME, m) {
+  m.def("fwd(Tensor! q, Tensor k, Tensor v, Tensor? k_new, Tensor? v_new, Tensor? q_v, "
+        "Tensor!? out, Tensor? cu_seqlens_q, Tensor? cu_seqlens_k, Tensor? cu_seqlens_k_new, "
+        "Tensor? seqused_q, Tensor? seqused_k, int? max_seqlen_q, int? max_seqlen_k, "
+        "Tensor? page_table, Tensor? kv_batch_idx, Tensor? leftpad_k, Tensor? rotary_cos, "
+        "Tensor? rotary_sin, Tensor? seqlens_rotary, Tensor? q_descale, Tensor? k_descale, "
+        "Tensor? v_descale, float softmax_scale, bool is_causal, int window_size_left, "
+        "int window_size_right, float softcap, bool is_rotary_interleaved, "
+        "Tensor? scheduler_metadata, int num_splits, bool? pack_gqa, int sm_margin, "
+        "Tensor? s_aux, int cp_world_size, int cp_rank, Tensor? cp_tot_seqused_k) -> Tensor[]");
+  m.impl("fwd", torch::kCUDA, &mha_fwd);
+  m.def("get_scheduler_metadata(int batch_size, int max_seqlen_q, int max_seqlen_k, "
+        "int num_heads, int num_heads_k, int headdim, int headdim_v, ScalarType qkv_dtype, "
+        "Tensor seqused_k, Tensor? cu_seqlens_q, Tensor? cu_seqlens_k, Tensor? cu_seqlens_k_new, "
+        "Tensor? seqused_q, Tensor? leftpad_k, int? page_size, int max_seqlen_k_new, "
+        "bool is_causal, int window_size_left, int window_size_right, bool has_softcap, "
+        "int num_splits, bool? pack_gqa, int sm_margin) -> Tensor");
+  m.impl("get_scheduler_metadata", torch::kCUDA, &mha_fwd_get_scheduler_metadata);
+}

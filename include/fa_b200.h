@@ -1,0 +1,140 @@
+/* fa_b200.h — C ABI of the B200 (sm_100a) FlashAttention-forward library `libfa_b200.so`.
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless its comment says host.
+ * No entry point allocates device memory, synchronises the stream, or throws; each returns 0
+ * (FA_OK) or one of the FA_ERR_* codes below, and launches on the stream it is given.
+ * The library never computes on the CPU: without a usable sm_100 device every compute entry point
+ * returns FA_ERR_NO_DEVICE.
+ *
+ * These entry points sit directly under the torch-op boundary of the reference
+ * (`fwd` / `get_scheduler_metadata`, kernels/fa4_blackwell.cu:10187-10205); citations below name the
+ * reference function each one replaces.
+ */
+#ifndef FA_B200_H_
+#define FA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* fa_stream_t; /* == cudaStream_t */
+
+enum {
+  FA_OK = 0,
+  FA_ERR_UNSUPPORTED = 1,   /* configuration outside the supported envelope ("unsupported") */
+  FA_ERR_BAD_ARG = 2,       /* inconsistent or missing argument */
+  FA_ERR_WORKSPACE = 3,     /* workspace too small */
+  FA_ERR_NO_DEVICE = 4,     /* no sm_100 device / driver entry point missing */
+  FA_ERR_LAUNCH = 5,        /* a CUDA call failed; see fa_b200_last_cuda_error() */
+  FA_ERR_DEVICE_TIMEOUT = 6 /* a bounded device-side wait ran out (read from the status word) */
+};
+
+enum { FA_DT_BF16 = 0, FA_DT_FP16 = 1, FA_DT_FP8_E4M3 = 2 };
+
+/* Which kernel family to use. AUTO routes by shape; the others force one family (testing, A/B). */
+enum { FA_ROUTE_AUTO = 0, FA_ROUTE_PREFILL_TC = 1, FA_ROUTE_DECODE = 2, FA_ROUTE_GENERAL = 3 };
+
+/* One attention-forward problem. Strides are in ELEMENTS. Replaces the argument list of
+ * `mha_fwd` (kernels/fa4_blackwell.cu:10081-10094) after tensor unpacking. */
+typedef struct FaFwdParams {
+  /* ---- tensors ---- */
+  const void* q;            /* (total_q, hq, hd) */
+  const void* k;            /* non-paged (total_k, hkv, hd); paged (num_pages, page_size, hkv, hd) */
+  const void* v;            /* non-paged (total_k, hkv, hdv); paged (num_pages, page_size, hkv, hdv) */
+  void* out;                /* (total_q, hq, hdv); element type out_dtype */
+  float* lse;               /* (hq, total_q) fp32, natural log; -inf for rows that see nothing */
+  int64_t q_row_stride, q_head_stride;
+  int64_t k_row_stride, k_head_stride, k_page_stride; /* row = one token; page stride only when paged */
+  int64_t v_row_stride, v_head_stride, v_page_stride;
+  int64_t o_row_stride, o_head_stride;
+  const int32_t* cu_seqlens_q;  /* (batch+1), required */
+  const int32_t* cu_seqlens_k;  /* (batch+1), non-paged */
+  const int32_t* seqused_k;     /* (batch), paged (optional override when non-paged) */
+  const int32_t* page_table;    /* (batch, page_table_stride) physical page of each logical page, or NULL */
+  const int32_t* leftpad_k;     /* (batch) keys with index < leftpad_k[b] are ignored, or NULL */
+  const float* q_descale;       /* fp8: (batch, hkv) via the two strides below, or NULL */
+  const float* k_descale;
+  const float* v_descale;
+  const float* s_aux;           /* (hq) fp32 sink logits or NULL */
+  const int32_t* scheduler_metadata; /* output of fa_b200_get_scheduler_metadata for this problem, or NULL */
+  /* ---- sizes ---- */
+  int32_t batch, total_q, total_k, hq, hkv, hd, hdv;
+  int32_t max_seqlen_q, max_seqlen_k;      /* upper bounds known on the host (0 = unknown: not allowed) */
+  int32_t page_size, num_pages, page_table_stride;
+  int32_t descale_batch_stride, descale_head_stride; /* 0,0 broadcasts a scalar */
+  int32_t q_dtype, kv_dtype, out_dtype;    /* FA_DT_* */
+  /* ---- semantics ---- */
+  float softmax_scale;
+  float softcap;                           /* 0 = off */
+  int32_t is_causal;                       /* bottom-right aligned: qpos = seqlen_k - seqlen_q + row */
+  int32_t window_left, window_right;       /* -1 = unbounded */
+  /* ---- scheduling ---- */
+  int32_t num_splits;                      /* 0 = heuristic, 1 = never split, >1 = at most that many */
+  int32_t sm_margin;                       /* SMs to leave free */
+  int32_t route;                           /* FA_ROUTE_* */
+} FaFwdParams;
+
+/* Bytes of scratch fa_b200_fwd needs for `p` (split partials, work list, status word). Host-only
+ * arithmetic. The caller allocates it (256-byte aligned) and may reuse it across calls on one stream.
+ * Replaces the per-call `at::empty` scratch of `launch_ws_paged` (kernels/fa4_blackwell.cu:9737-9738). */
+size_t fa_b200_fwd_workspace_bytes(const FaFwdParams* p);
+
+/* Attention forward. Replaces `mha_fwd`'s routing and launches (kernels/fa4_blackwell.cu:10138-10169:
+ * launch_ws / launch_paged_maybe_split / launch, and combine_kernel 5964-5985 after a split launch). */
+int fa_b200_fwd(const FaFwdParams* p, void* workspace, size_t workspace_bytes, fa_stream_t stream);
+
+/* The split count fa_b200_fwd will use for `p` (>= 1). Host-only arithmetic; restates the role of the
+ * split heuristic in `launch_ws_paged` (kernels/fa4_blackwell.cu:9721-9735). */
+int fa_b200_num_splits(const FaFwdParams* p);
+
+/* Scheduler metadata. Replaces `mha_fwd_get_scheduler_metadata` (kernels/fa4_blackwell.cu:10175-10183,
+ * a stub there). The arguments mirror that op's. */
+typedef struct FaSchedParams {
+  const int32_t* seqused_k;     /* (batch) or NULL */
+  const int32_t* cu_seqlens_q;  /* (batch+1) or NULL => every sequence has max_seqlen_q rows */
+  const int32_t* cu_seqlens_k;  /* (batch+1) or NULL */
+  const int32_t* leftpad_k;     /* (batch) or NULL */
+  int32_t batch, max_seqlen_q, max_seqlen_k, hq, hkv, hd, hdv;
+  int32_t qkv_dtype;            /* FA_DT_* */
+  int32_t page_size;            /* 0 = not paged */
+  int32_t is_causal, window_left, window_right, has_softcap;
+  int32_t num_splits, sm_margin;
+} FaSchedParams;
+
+/* Number of int32 words of the metadata tensor for `p` (host arithmetic). */
+int fa_b200_scheduler_metadata_len(const FaSchedParams* p);
+/* Fills `out_dev` (device, fa_b200_scheduler_metadata_len words) on `stream`. */
+int fa_b200_get_scheduler_metadata(const FaSchedParams* p, int32_t* out_dev, fa_stream_t stream);
+
+/* LSE-weighted merge of `nsplits` partial results; also the merge step of the multi-GPU KV-range
+ * sharding. Replaces `combine_kernel` (kernels/fa4_blackwell.cu:5964-5985).
+ *   o_part   (nsplits, total_q, hq, hdv) fp32, each split normalised by its own denominator
+ *   lse_part (nsplits, hq, total_q)      fp32 natural log, -inf for a split that saw no key
+ *   s_aux    (hq) fp32 sink logits or NULL (the sink joins exactly once, here)
+ *   out      (total_q, hq, hdv) with the given strides, out_dtype FA_DT_BF16/FP16
+ *   lse      (hq, total_q) fp32 */
+int fa_b200_combine(const float* o_part, const float* lse_part, int32_t nsplits, int32_t total_q,
+                    int32_t hq, int32_t hdv, const float* s_aux, void* out, int64_t o_row_stride,
+                    int64_t o_head_stride, int32_t out_dtype, float* lse, fa_stream_t stream);
+
+/* Reads the device status word of a workspace after synchronising `stream` (the only entry point that
+ * synchronises). Returns FA_OK, or FA_ERR_DEVICE_TIMEOUT with *detail = (role<<24 | block) of the first
+ * wait that gave up. The reference has no counterpart: its device waits are unbounded
+ * (kernels/fa4_blackwell.cu:5732). */
+int fa_b200_check_status(void* workspace, fa_stream_t stream, uint32_t* detail /* host, may be NULL */);
+
+const char* fa_b200_strerror(int code);      /* host string */
+const char* fa_b200_last_cuda_error(void);   /* host string of the last failed CUDA call on this thread */
+int fa_b200_version(void);
+/* sizeof(FaFwdParams) / sizeof(FaSchedParams) as this library was compiled: lets a foreign-function
+ * binding verify its own struct layout before the first call. No counterpart in the reference. */
+size_t fa_b200_sizeof_fwd_params(void);
+size_t fa_b200_sizeof_sched_params(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FA_B200_H_ */

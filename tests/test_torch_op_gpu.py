@@ -1,0 +1,56 @@
+"""The drop-in boundary on a GPU: the `fwd` / `get_scheduler_metadata` torch ops, called with the
+reference harness' positional argument order (bench/scenarios.py:910-929)."""
+import pytest
+import torch
+
+import _golden
+from flash_cuda_b200 import ops
+from oracle.ref_attention import ref_attention
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("name", ["g_dense_nc_mha", "g_causal_gqa_mix", "g_win_cap_sink", "g_paged_decode_leftpad",
+                                  "g_paged_spec_q4", "g_fp8_qkv_causal", "g_fp8kv_paged_decode", "g_hd192_dv128"])
+def test_fwd_op_matches_reference_numbers(name, cuda_device):
+    d = _golden.load(name)
+    res = ops.fwd(*_golden.fwd_args(d, cuda_device))
+    assert len(res) == 4 and res[2].numel() == 0 and res[3].numel() == 0
+    out, lse = res[0], res[1]
+    total_q, hq = d["q"].shape[0], d["q"].shape[1]
+    assert out.shape == d["ref_out"].shape and lse.shape == (hq, total_q) and lse.dtype == torch.float32
+    assert out.dtype == (torch.bfloat16 if d["q"].dtype == torch.float8_e4m3fn else d["q"].dtype)
+    tol = 6e-2 if d["k"].dtype == torch.float8_e4m3fn else 2e-2
+    assert (out.float().cpu() - d["ref_out"]).abs().max().item() <= tol
+    _, ref_lse = ref_attention(d["q"], d["k"], d["v"], **_golden.oracle_kwargs(d))
+    fin = torch.isfinite(ref_lse)
+    torch.testing.assert_close(lse.cpu()[fin], ref_lse[fin], atol=5e-3, rtol=1e-2)
+
+
+def test_out_argument_is_written_in_place(cuda_device):
+    d = _golden.load("g_dense_nc_mha")
+    out = torch.full(d["ref_out"].shape, 7.0, device=cuda_device, dtype=torch.bfloat16)
+    res = ops.fwd(*_golden.fwd_args(d, cuda_device, out=out))
+    assert res[0].data_ptr() == out.data_ptr()
+    assert (out.float().cpu() - d["ref_out"]).abs().max().item() <= 2e-2
+
+
+def test_unsupported_raises_with_the_word_unsupported(cuda_device):
+    q = torch.randn(8, 2, 100, device=cuda_device, dtype=torch.bfloat16)
+    cu = torch.tensor([0, 8], device=cuda_device, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="unsupported"):
+        ops.call_fwd(q, q, q, cu_seqlens_q=cu, cu_seqlens_k=cu, max_seqlen_q=8, max_seqlen_k=8,
+                     softmax_scale=0.1, causal=True)
+
+
+def test_scheduler_metadata_round_trip(cuda_device):
+    d = _golden.load("g_paged_decode_p64_sink")
+    cfg = d["cfg"]
+    hq, hd = d["q"].shape[1], d["q"].shape[2]
+    md = ops.get_scheduler_metadata(
+        len(d["seqused_k"]), d["max_seqlen_q"], d["max_seqlen_k"], hq, d["k"].shape[2], hd, d["v"].shape[3],
+        torch.bfloat16, d["seqused_k"].to(cuda_device), d["cu_seqlens_q"].to(cuda_device), None, None, None, None,
+        d["k"].shape[1], 0, True, -1, -1, False, 0, None, 0)
+    assert md.dtype == torch.int32 and md.numel() >= 16
+    res = ops.fwd(*_golden.fwd_args(d, cuda_device, scheduler_metadata=md))
+    assert (res[0].float().cpu() - d["ref_out"]).abs().max().item() <= 2e-2
