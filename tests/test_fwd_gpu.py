@@ -137,3 +137,32 @@ def test_unsupported_is_an_error_not_a_fallback(cuda_device):
     with pytest.raises(capi.FaError) as ei:
         capi.fwd(p.q, p.k, p.v, **p.capi_kw())
     assert ei.value.code == capi.FA_ERR_UNSUPPORTED and "unsupported" in str(ei.value)
+
+
+@pytest.mark.parametrize("case", [
+    dict(reqs=[(1, 700), (1, 64), (1, 6500), (1, 1), (1, 1000), (1, 6400)], hq=8, hkv=2, page_size=64,
+         leftpad=[63, 0, 17, 0, 640, 128], causal=True, wl=-1, wr=-1),
+    dict(reqs=[(300, 300), (17, 900), (128, 128), (64, 64)], hq=4, hkv=4, page_size=0, leftpad=None, causal=True,
+         wl=100, wr=0),
+    dict(reqs=[(5, 40), (70, 333)], hq=4, hkv=1, page_size=0, leftpad=None, causal=False, wl=20, wr=11),
+])
+def test_scheduler_metadata_is_bit_exact(case, cuda_device):
+    """Integer output: every word equals the CPU restatement."""
+    from oracle import sched_oracle as SO
+    reqs = case["reqs"]
+    q_lens, k_lens = [a for a, _ in reqs], [b for _, b in reqs]
+    B = len(reqs)
+    cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=cuda_device)
+    seqused = torch.tensor(k_lens, dtype=torch.int32, device=cuda_device)
+    lp = None if case["leftpad"] is None else torch.tensor(case["leftpad"], dtype=torch.int32, device=cuda_device)
+    shape = dict(batch=B, max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens), hq=case["hq"], hkv=case["hkv"],
+                 hd=128, hdv=128, page_size=case["page_size"])
+    md = capi.get_scheduler_metadata(cuda_device, dtype=torch.bfloat16, seqused_k=seqused, cu_seqlens_q=cu_q,
+                                     leftpad_k=lp, causal=case["causal"], window_left=case["wl"],
+                                     window_right=case["wr"], **shape)
+    sms = torch.cuda.get_device_properties(cuda_device).multi_processor_count
+    plan = SO.make_plan(num_sms_device=sms, **shape)
+    want = SO.scheduler_metadata(plan, batch=B, max_seqlen_q=max(q_lens), max_seqlen_k=max(k_lens), q_lens=q_lens,
+                                 k_lens=k_lens, leftpad=case["leftpad"], causal=case["causal"],
+                                 window_left=case["wl"], window_right=case["wr"])
+    assert md.cpu().tolist() == want
