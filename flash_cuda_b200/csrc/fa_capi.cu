@@ -18,6 +18,7 @@ int launch_decode(const KParams& kp, const Plan& pl, int compute_dtype, cudaStre
 int launch_prefill_tc(const KParams& kp, const Plan& pl, int compute_dtype, cudaStream_t stream);
 bool prefill_tc_supported(const PlanInput& in);
 bool decode_supported(const PlanInput& in);
+bool prefill_tc_layout_ok(const FaFwdParams* p);
 
 static thread_local char g_last_cuda_error[256] = "";
 
@@ -83,7 +84,7 @@ Plan make_plan(const PlanInput& in) {
   }
   const int rep = in.hq / in.hkv;
   int route = in.route;
-  const bool tc_ok = prefill_tc_supported(in), dec_ok = decode_supported(in);
+  const bool tc_ok = prefill_tc_supported(in) && in.tc_layout_ok, dec_ok = decode_supported(in);
   if (route == FA_ROUTE_AUTO) {
     if (dec_ok && in.max_seqlen_q * rep <= 64) route = FA_ROUTE_DECODE;
     else if (tc_ok) route = FA_ROUTE_PREFILL_TC;
@@ -109,7 +110,7 @@ Plan make_plan(const PlanInput& in) {
   const long heads = pl.rows_per_token > 1 ? in.hkv : in.hq;
   const long ctas = (long)in.batch * heads * pl.max_mtiles;
   int s = 1;
-  if (in.num_splits == 1) {
+  if (route == FA_ROUTE_PREFILL_TC || in.num_splits == 1) {   // the tensor-core prefill route never splits
     s = 1;
   } else if (in.num_splits > 1) {
     s = in.num_splits < max_nb ? in.num_splits : max_nb;
@@ -135,6 +136,7 @@ static PlanInput plan_input(const FaFwdParams* p, int num_sms) {
   in.has_softcap = p->softcap > 0.f;
   in.num_splits = p->num_splits; in.sm_margin = p->sm_margin; in.route = p->route;
   in.num_sms_device = num_sms;
+  in.tc_layout_ok = prefill_tc_layout_ok(p) ? 1 : 0;
   return in;
 }
 static PlanInput plan_input(const FaSchedParams* p, int num_sms) {
@@ -148,6 +150,7 @@ static PlanInput plan_input(const FaSchedParams* p, int num_sms) {
   in.has_softcap = p->has_softcap;
   in.num_splits = p->num_splits; in.sm_margin = p->sm_margin; in.route = FA_ROUTE_AUTO;
   in.num_sms_device = num_sms;
+  in.tc_layout_ok = 1;
   return in;
 }
 
@@ -270,7 +273,7 @@ int fa_b200_fwd(const FaFwdParams* p, void* workspace, size_t workspace_bytes, f
   kp.k_row_stride = p->k_row_stride; kp.k_head_stride = p->k_head_stride; kp.k_page_stride = p->k_page_stride;
   kp.v_row_stride = p->v_row_stride; kp.v_head_stride = p->v_head_stride; kp.v_page_stride = p->v_page_stride;
   kp.o_row_stride = p->o_row_stride; kp.o_head_stride = p->o_head_stride;
-  kp.batch = p->batch; kp.total_q = p->total_q; kp.hq = p->hq; kp.hkv = p->hkv; kp.rep = p->hq / p->hkv;
+  kp.batch = p->batch; kp.total_q = p->total_q; kp.total_k = p->total_k; kp.num_pages = p->num_pages; kp.hq = p->hq; kp.hkv = p->hkv; kp.rep = p->hq / p->hkv;
   kp.hd = p->hd; kp.hdv = p->hdv;
   kp.max_seqlen_q = p->max_seqlen_q; kp.max_seqlen_k = p->max_seqlen_k;
   kp.page_size = p->page_table ? p->page_size : 0;

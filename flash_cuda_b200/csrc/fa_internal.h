@@ -34,7 +34,7 @@ struct KParams {
   int64_t k_row_stride, k_head_stride, k_page_stride;
   int64_t v_row_stride, v_head_stride, v_page_stride;
   int64_t o_row_stride, o_head_stride;
-  int32_t batch, total_q, hq, hkv, rep, hd, hdv;
+  int32_t batch, total_q, total_k, num_pages, hq, hkv, rep, hd, hdv;
   int32_t max_seqlen_q, max_seqlen_k;
   int32_t page_size, page_shift /* log2(page_size) or -1 */, page_table_stride;
   int32_t descale_batch_stride, descale_head_stride;

@@ -1,7 +1,621 @@
-// placeholder until the tcgen05 prefill kernel lands
+// fa_prefill_tc.cu — the prefill mainloop on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
+//
+// One persistent CTA per SM.  A work item is a pair of adjacent 128-row query tiles of one (batch, q head);
+// both tiles share every K/V tile that TMA brings in.  Warp roles (320 threads):
+//   warps 0-3  softmax of tile 0   (one query row per thread: S row TMEM -> registers -> P row TMEM)
+//   warps 4-7  softmax of tile 1
+//   warp  8    MMA issuer: S_t = Q_t K^T (operands in shared memory), O_t += P_t V (P in TMEM)
+//   warp  9    TMA producer: Q pair, K ring, V ring (no cluster multicast: each CTA loads its own tiles)
+// TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t overlays the first 64
+// columns of S_t once the owning thread has read its S row.
+// The tensor pipe runs [PV0(i), QK0(i+1), PV1(i), QK1(i+1)] so that one tile's softmax overlaps the other
+// tile's MMAs.  Softmax works in the exp2 domain with a lazy maximum: the running maximum only moves (and
+// O is only rescaled) when the new row maximum exceeds it by more than 8.
+// Every wait is bounded: on expiry the role records an error in the status word, raises a CTA-wide abort
+// flag, and every role drains and leaves.
+//
+// Plays the role of `fwd_kernel_fa4` / `fwd_kernel_ws2` / `fwd_kernel_fa4dk` of the reference
+// (kernels/fa4_blackwell.cu:6935-7407, 6539-6906, 7420-7753) with masks, softcap, sink, leftpad, paged KV
+// and head_dim 192/128 in the one kernel.
+#include <cuda.h>
+
+#include <mutex>
+
 #include "fa_internal.h"
 #include "fa_sched.h"
+#include "ptx.cuh"
+
 namespace fa {
-bool prefill_tc_supported(const PlanInput&) { return false; }
-int launch_prefill_tc(const KParams&, const Plan&, int, cudaStream_t) { return -1; }
+namespace tc {
+
+constexpr int TM = 128, TN = 128;
+constexpr int NTHREADS = 320;
+constexpr int WARP_MMA = 8, WARP_TMA = 9;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;   // log2 units
+enum Role : unsigned { ROLE_TMA = 1, ROLE_MMA = 2, ROLE_SOFTMAX = 3, ROLE_EPILOGUE = 4 };
+
+struct TcArgs {
+  KParams kp;
+  int num_items;     // batch * hq * max_pairs
+  int max_pairs;
+  int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128)
+  int kv_total_rows; // rows of the K/V tensor map (out-of-range y => zero fill)
+};
+
+template <int HD, int HDV, int KST, int VST>
+struct Smem {
+  static constexpr int kQBytes = 2 * TM * HD * 2;
+  static constexpr int kKStage = TN * HD * 2;
+  static constexpr int kVStage = TN * HDV * 2;
+  static constexpr int kBarOff = kQBytes + KST * kKStage + VST * kVStage;
+  static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1;
+  static constexpr int kBytes = kBarOff + kNumBars * 8 + 16;
+};
+
+// All roles derive the same tile geometry from the same inputs.
+struct Item {
+  int b, h, pair;
+  int q0, seqlen_q, seqlen_k, k0, leftpad;
+  int lo[2], hi[2];   // key-block range per tile
+  int ulo, uhi;       // union
+  bool valid;
+};
+
+__device__ __forceinline__ Item decode_item(const TcArgs& a, int w) {
+  const KParams& p = a.kp;
+  Item it;
+  const int per_slot = p.batch * p.hq;
+  const int slot = w / per_slot, rem = w - slot * per_slot;
+  it.pair = a.max_pairs - 1 - slot;          // heavy (late) tiles first under causal masking
+  it.b = rem / p.hq;
+  it.h = rem - it.b * p.hq;
+  it.q0 = p.cu_q[it.b];
+  it.seqlen_q = p.cu_q[it.b + 1] - it.q0;
+  it.k0 = p.page_table ? 0 : p.cu_k[it.b];
+  it.seqlen_k = p.seqused_k ? p.seqused_k[it.b] : (p.cu_k[it.b + 1] - p.cu_k[it.b]);
+  it.leftpad = p.leftpad_k ? p.leftpad_k[it.b] : 0;
+  it.valid = it.pair * 2 * TM < it.seqlen_q;
+  it.ulo = 0x7fffffff;
+  it.uhi = 0;
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const int row0 = it.pair * 2 * TM + t * TM;
+    it.lo[t] = it.hi[t] = 0;
+    if (it.valid && row0 < it.seqlen_q) {
+      const int rmax = min(it.seqlen_q - 1, row0 + TM - 1);
+      nblock_range(it.seqlen_k, it.leftpad, it.seqlen_k - it.seqlen_q + row0, it.seqlen_k - it.seqlen_q + rmax,
+                   p.is_causal, p.window_left, p.window_right, TN, &it.lo[t], &it.hi[t]);
+    }
+    if (it.hi[t] > it.lo[t]) { it.ulo = min(it.ulo, it.lo[t]); it.uhi = max(it.uhi, it.hi[t]); }
+  }
+  if (it.uhi <= it.ulo) { it.ulo = it.uhi = 0; }
+  return it;
+}
+
+// Bounded wait that also gives up when another role has raised the abort flag.
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+#pragma unroll 1
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > 2000000000ull) return false;   // 2 s
+  }
+}
+
+template <typename T, int HD, int HDV, int KST, int VST>
+__global__ void __launch_bounds__(NTHREADS, 1)
+fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
+                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+  using SM = Smem<HD, HDV, KST, VST>;
+  const KParams& p = a.kp;
+  extern __shared__ unsigned char smem_dyn[];
+  // 1024-byte alignment for the 128-byte swizzle atoms
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* sm = smem_dyn + (base - raw);
+  const uint32_t sQ = base;
+  const uint32_t sK = sQ + SM::kQBytes;
+  const uint32_t sV = sK + KST * SM::kKStage;
+  const uint32_t bars = base + SM::kBarOff;
+  // barrier map
+  const uint32_t bar_q_full = bars, bar_q_empty = bars + 8;
+  const uint32_t bar_k_full = bars + 16, bar_k_empty = bar_k_full + 8 * KST;
+  const uint32_t bar_v_full = bar_k_empty + 8 * KST, bar_v_empty = bar_v_full + 8 * VST;
+  const uint32_t bar_s_full = bar_v_empty + 8 * VST;     // [2]
+  const uint32_t bar_p_full = bar_s_full + 16;           // [2]
+  const uint32_t bar_o_full = bar_p_full + 16;           // [2]
+  const uint32_t bar_o_empty = bar_o_full + 16;          // [2]
+  const uint32_t bar_drain = bar_o_empty + 16;           // MMA warp's private drain barrier
+  volatile int* s_abort = reinterpret_cast<volatile int*>(sm + SM::kBarOff + SM::kNumBars * 8);
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sm + SM::kBarOff + SM::kNumBars * 8 + 8);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    mbar_init(bar_q_full, 1); mbar_init(bar_q_empty, 1);
+    for (int s = 0; s < KST; ++s) { mbar_init(bar_k_full + 8 * s, 1); mbar_init(bar_k_empty + 8 * s, 1); }
+    for (int s = 0; s < VST; ++s) { mbar_init(bar_v_full + 8 * s, 1); mbar_init(bar_v_empty + 8 * s, 1); }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(bar_s_full + 8 * t, 1); mbar_init(bar_p_full + 8 * t, 128);
+      mbar_init(bar_o_full + 8 * t, 1); mbar_init(bar_o_empty + 8 * t, 128);
+    }
+    mbar_init(bar_drain, 1);
+    s_abort[0] = 0;
+    s_abort[1] = 0;   // [1] is never raised: waits that may only end by completion or time limit
+    mbar_fence_init();
+  }
+  if (warp == WARP_MMA) { tmem_alloc(smem_u32(s_tmem), 512); tmem_relinquish(); }
+  if (warp == WARP_TMA && lane == 0) { tma_prefetch_desc(&map_q); tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *s_tmem;
+
+  if (warp == WARP_TMA) {
+    // =========================================== TMA producer ===========================================
+    if (lane == 0) {
+      uint32_t qcnt = 0, kcnt = 0, vcnt = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < a.num_items && ok; w += gridDim.x) {
+        const Item it = decode_item(a, w);
+        if (!it.valid || it.uhi <= it.ulo) continue;
+        ok = wait_or_abort(bar_q_empty, (qcnt & 1) ^ 1, s_abort);
+        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+        mbar_expect_tx(bar_q_full, SM::kQBytes);
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+          for (int cb = 0; cb < HD / 64; ++cb)
+            tma_load_2d(sQ + t * (TM * HD * 2) + cb * (TM * 128), &map_q, it.h * HD + cb * 64,
+                        it.q0 + it.pair * 2 * TM + t * TM, bar_q_full);
+        ++qcnt;
+        const int hk = it.h / p.rep;
+        for (int nb = it.ulo; nb < it.uhi; ++nb) {
+          // K tile
+          {
+            const uint32_t s = kcnt % KST;
+            ok = wait_or_abort(bar_k_empty + 8 * s, ((kcnt / KST) & 1) ^ 1, s_abort);
+            if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+            mbar_expect_tx(bar_k_full + 8 * s, SM::kKStage);
+            const uint32_t dst = sK + s * SM::kKStage;
+            if (p.page_table == nullptr) {
+#pragma unroll
+              for (int cb = 0; cb < HD / 64; ++cb)
+                tma_load_2d(dst + cb * (TN * 128), &map_k, hk * HD + cb * 64, it.k0 + nb * TN, bar_k_full + 8 * s);
+            } else {
+              for (int r = 0; r < TN; r += a.kv_box_rows) {
+                const int kk = nb * TN + r;
+                int y = a.kv_total_rows;   // beyond the sequence: out of range => zeros
+                if (kk < it.seqlen_k) {
+                  const int lp = p.page_shift >= 0 ? (kk >> p.page_shift) : (kk / p.page_size);
+                  y = p.page_table[(int64_t)it.b * p.page_table_stride + lp] * p.page_size + (kk - lp * p.page_size);
+                }
+#pragma unroll
+                for (int cb = 0; cb < HD / 64; ++cb)
+                  tma_load_2d(dst + cb * (TN * 128) + r * 128, &map_k, hk * HD + cb * 64, y, bar_k_full + 8 * s);
+              }
+            }
+            ++kcnt;
+          }
+          // V tile
+          {
+            const uint32_t s = vcnt % VST;
+            ok = wait_or_abort(bar_v_empty + 8 * s, ((vcnt / VST) & 1) ^ 1, s_abort);
+            if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+            mbar_expect_tx(bar_v_full + 8 * s, SM::kVStage);
+            const uint32_t dst = sV + s * SM::kVStage;
+            if (p.page_table == nullptr) {
+#pragma unroll
+              for (int cb = 0; cb < HDV / 64; ++cb)
+                tma_load_2d(dst + cb * (TN * 128), &map_v, hk * HDV + cb * 64, it.k0 + nb * TN, bar_v_full + 8 * s);
+            } else {
+              for (int r = 0; r < TN; r += a.kv_box_rows) {
+                const int kk = nb * TN + r;
+                int y = a.kv_total_rows;
+                if (kk < it.seqlen_k) {
+                  const int lp = p.page_shift >= 0 ? (kk >> p.page_shift) : (kk / p.page_size);
+                  y = p.page_table[(int64_t)it.b * p.page_table_stride + lp] * p.page_size + (kk - lp * p.page_size);
+                }
+#pragma unroll
+                for (int cb = 0; cb < HDV / 64; ++cb)
+                  tma_load_2d(dst + cb * (TN * 128) + r * 128, &map_v, hk * HDV + cb * 64, y, bar_v_full + 8 * s);
+              }
+            }
+            ++vcnt;
+          }
+        }
+      }
+      if (!ok) *s_abort = 1;
+      // drain: every copy this thread issued must have landed before the CTA may leave
+      if (qcnt > 0) wait_or_abort(bar_q_full, (qcnt - 1) & 1, s_abort + 1 /* never set: pure time limit */);
+      for (uint32_t s = 0; s < (uint32_t)KST; ++s) {
+        if (kcnt > s) { const uint32_t last = (kcnt - 1 - s) / KST; wait_or_abort(bar_k_full + 8 * s, last & 1, s_abort + 1); }
+      }
+      for (uint32_t s = 0; s < (uint32_t)VST; ++s) {
+        if (vcnt > s) { const uint32_t last = (vcnt - 1 - s) / VST; wait_or_abort(bar_v_full + 8 * s, last & 1, s_abort + 1); }
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    // =========================================== MMA issuer =============================================
+    constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+    constexpr uint32_t idesc_qk = umma_idesc(kFmt, TM, TN, false);
+    constexpr uint32_t idesc_pv = umma_idesc(kFmt, TM, HDV, true);
+    uint32_t qcnt = 0, kcnt = 0, vcnt = 0, pcnt[2] = {0, 0}, oecnt[2] = {0, 0};
+    bool ok = true;
+    const bool leader = lane == 0;
+
+    auto issue_qk = [&](int t, uint32_t kslot) {
+      if (leader) {
+        const uint32_t qa = sQ + t * (TM * HD * 2), ka = sK + kslot * SM::kKStage;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * (TM * 128) + (ks & 3) * 32;
+          umma_ss<false>(tmem + t * TN, umma_desc(qa + off, 16, 1024), umma_desc(ka + off, 16, 1024), idesc_qk,
+                         ks > 0 ? 1u : 0u);
+        }
+        umma_commit(bar_s_full + 8 * t);
+      }
+    };
+    auto issue_pv = [&](int t, uint32_t vslot, bool first) {
+      if (leader) {
+        const uint32_t va = sV + vslot * SM::kVStage;
+#pragma unroll
+        for (int ks = 0; ks < TN / 16; ++ks)
+          umma_ts<false>(tmem + 256 + t * 128, tmem + t * TN + ks * 8, umma_desc(va + ks * 2048, TN * 128, 1024),
+                         idesc_pv, (!first || ks > 0) ? 1u : 0u);
+      }
+    };
+
+    for (int w = blockIdx.x; w < a.num_items && ok; w += gridDim.x) {
+      const Item it = decode_item(a, w);
+      if (!it.valid || it.uhi <= it.ulo) continue;
+      ok = wait_or_abort(bar_q_full, qcnt & 1, s_abort);
+      ++qcnt;
+      if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
+      // prologue: QK of the first block
+      {
+        const uint32_t ks = kcnt % KST;
+        ok = wait_or_abort(bar_k_full + 8 * ks, (kcnt / KST) & 1, s_abort);
+        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
+        tc_fence_after_sync();
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+          if (it.ulo >= it.lo[t] && it.ulo < it.hi[t]) issue_qk(t, ks);
+        if (leader) umma_commit(bar_k_empty + 8 * ks);
+        ++kcnt;
+      }
+      for (int i = it.ulo; i < it.uhi && ok; ++i) {
+        const bool nxt = i + 1 < it.uhi;
+        const uint32_t vs = vcnt % VST;
+        const uint32_t ks = kcnt % KST;       // slot of block i+1 (if any)
+        ok = wait_or_abort(bar_v_full + 8 * vs, (vcnt / VST) & 1, s_abort);
+        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
+        bool k_ready = false;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (i >= it.lo[t] && i < it.hi[t]) {
+            const bool first = i == it.lo[t];
+            if (first) {   // O_t is overwritten: the previous item's epilogue must have read it
+              ok = wait_or_abort(bar_o_empty + 8 * t, (oecnt[t] & 1) ^ 1, s_abort);
+              ++oecnt[t];
+              if (!ok) break;
+            }
+            ok = wait_or_abort(bar_p_full + 8 * t, pcnt[t] & 1, s_abort);
+            ++pcnt[t];
+            if (!ok) break;
+            tc_fence_after_sync();
+            issue_pv(t, vs, first);
+            if (i + 1 == it.hi[t] && leader) umma_commit(bar_o_full + 8 * t);
+          }
+          if (nxt && i + 1 >= it.lo[t] && i + 1 < it.hi[t]) {
+            if (!k_ready) {
+              ok = wait_or_abort(bar_k_full + 8 * ks, (kcnt / KST) & 1, s_abort);
+              if (!ok) break;
+              tc_fence_after_sync();
+              k_ready = true;
+            }
+            issue_qk(t, ks);
+          }
+        }
+        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
+        if (leader) umma_commit(bar_v_empty + 8 * vs);
+        ++vcnt;
+        if (nxt) {
+          if (!k_ready) {   // block i+1 belongs to neither tile: still consume its K slot
+            ok = wait_or_abort(bar_k_full + 8 * ks, (kcnt / KST) & 1, s_abort);
+            if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
+          }
+          if (leader) umma_commit(bar_k_empty + 8 * ks);
+          ++kcnt;
+        }
+      }
+      if (ok && leader) umma_commit(bar_q_empty);
+    }
+    if (!ok) *s_abort = 1;
+    // drain: all MMAs this warp issued must have retired before TMEM is released
+    if (leader) umma_commit(bar_drain);
+    wait_or_abort(bar_drain, 0, s_abort + 1);
+  } else {
+    // ========================================= softmax + epilogue =======================================
+    const int t = warp >> 2;                       // tile of this warpgroup
+    const int r = (warp & 3) * 32 + lane;          // row within the tile == TMEM lane
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tS = tmem + lane_base + t * TN;
+    const uint32_t tO = tmem + lane_base + 256 + t * 128;
+    const bool has_cap = p.softcap > 0.f;
+    uint32_t scnt = 0, ocnt = 0;
+    bool ok = true;
+
+    for (int w = blockIdx.x; w < a.num_items && ok; w += gridDim.x) {
+      const Item it = decode_item(a, w);
+      if (!it.valid) continue;
+      const int row0 = it.pair * 2 * TM + t * TM;
+      if (row0 >= it.seqlen_q) continue;           // this tile owns no row
+      const int row = row0 + r;
+      const int hk = it.h / p.rep;
+      float sc = p.scale, vds = 1.f;
+      {
+        const int di = it.b * p.descale_batch_stride + hk * p.descale_head_stride;
+        if (p.q_descale) sc *= p.q_descale[di];
+        if (p.k_descale) sc *= p.k_descale[di];
+        if (p.v_descale) vds = p.v_descale[di];
+      }
+      const float c_mul = has_cap ? p.softcap * kLog2e : sc * kLog2e;
+      const float cap_in = has_cap ? sc / p.softcap : 0.f;
+      const int qp = it.seqlen_k - it.seqlen_q + row;
+      int lo = it.leftpad, hi = it.seqlen_k - 1;
+      if (p.is_causal) hi = min(hi, qp);
+      if (p.window_right >= 0) hi = min(hi, qp + p.window_right);
+      if (p.window_left >= 0) lo = max(lo, qp - p.window_left);
+      // bounds that hold for every row of the tile (warpgroup-uniform): decide "no masking needed"
+      const int qp_first = it.seqlen_k - it.seqlen_q + row0, qp_last = qp_first + TM - 1;
+      int lo_max = it.leftpad, hi_min = it.seqlen_k - 1;
+      if (p.is_causal) hi_min = min(hi_min, qp_first);
+      if (p.window_right >= 0) hi_min = min(hi_min, qp_first + p.window_right);
+      if (p.window_left >= 0) lo_max = max(lo_max, qp_last - p.window_left);
+
+      float m_used = -INFINITY, l = 0.f;
+      for (int i = it.lo[t]; i < it.hi[t]; ++i) {
+        ok = wait_or_abort(bar_s_full + 8 * t, scnt & 1, s_abort);
+        ++scnt;
+        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_SOFTMAX); break; }
+        tc_fence_after_sync();
+        const int n0 = i * TN;
+        const bool full = (n0 >= lo_max) && (n0 + TN - 1 <= hi_min);
+        uint32_t sreg[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sreg[c]);
+        tmem_wait_ld();
+        float mx = -INFINITY;
+        if (has_cap) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              sreg[c][j] = __float_as_uint(tanh_fast(__uint_as_float(sreg[c][j]) * cap_in));
+        }
+        if (!full) {
+          const int rlo = lo - n0, rhi = hi - n0;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int col = c * 32 + j;
+              if (col < rlo || col > rhi) sreg[c][j] = 0xff800000u;   // -inf
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(sreg[c][j]));
+        const float y_max = mx * c_mul;               // c_mul > 0, so the maximum commutes with the scale
+        float corr = 1.f;
+        bool rescale = false;
+        if (m_used == -INFINITY) {
+          m_used = y_max;                             // first block with a visible key (may stay -inf)
+        } else if (y_max > m_used + kRescaleThreshold) {
+          corr = ex2(m_used - y_max);
+          m_used = y_max;
+          l *= corr;
+          rescale = true;
+        }
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        float psum = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const float p0 = ex2(fmaf(__uint_as_float(sreg[c][j]), c_mul, neg_m));
+            const float p1 = ex2(fmaf(__uint_as_float(sreg[c][j + 1]), c_mul, neg_m));
+            psum += p0 + p1;
+            pk[j >> 1] = pack2<T>(p0, p1);
+          }
+          tmem_st16(tS + c * 16, pk);
+        }
+        l += psum;
+        if (__any_sync(0xffffffffu, rescale)) {
+          // O_t of the previous blocks is complete: the commit behind s_full also covered PV_t(i-1)
+#pragma unroll 1
+          for (int c = 0; c < HDV / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tO + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __float_as_uint(__uint_as_float(o[j]) * corr);
+            tmem_st32(tO + c * 32, o);
+          }
+        }
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar_p_full + 8 * t);
+      }
+      if (!ok) break;
+
+      // ---- epilogue of this tile ----
+      const bool had_blocks = it.hi[t] > it.lo[t];
+      if (had_blocks) {
+        ok = wait_or_abort(bar_o_full + 8 * t, ocnt & 1, s_abort);
+        ++ocnt;
+        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_EPILOGUE); break; }
+        tc_fence_after_sync();
+      }
+      float m_fin = m_used, l_fin = l, osc = 1.f;
+      if (p.s_aux) {
+        const float ys = p.s_aux[it.h] * kLog2e;
+        const float mn = fmaxf(m_used, ys);
+        osc = (m_used == -INFINITY) ? 0.f : ex2(m_used - mn);
+        l_fin = l * osc + ex2(ys - mn);
+        m_fin = mn;
+      }
+      const float inv = l_fin > 0.f ? osc * vds / l_fin : 0.f;
+      const bool row_ok = row < it.seqlen_q;
+      T* op = reinterpret_cast<T*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
+#pragma unroll 1
+      for (int c = 0; c < HDV / 32; ++c) {
+        uint32_t o[32];
+        if (had_blocks) {
+          tmem_ld32(tO + c * 32, o);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = 0u;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 v;
+            v.x = pack2<T>(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
+            v.y = pack2<T>(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+            v.z = pack2<T>(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+            v.w = pack2<T>(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
+            *reinterpret_cast<uint4*>(op + c * 32 + j) = v;
+          }
+        }
+      }
+      if (had_blocks) {
+        tc_fence_before_sync();
+        mbar_arrive(bar_o_empty + 8 * t);
+      }
+      if (row_ok)
+        p.lse[(int64_t)it.h * p.total_q + it.q0 + row] = l_fin > 0.f ? (m_fin + lg2(l_fin)) * kLn2 : -INFINITY;
+    }
+    if (!ok) *s_abort = 1;
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == WARP_MMA) { tc_fence_after_sync(); tmem_dealloc(tmem, 512); }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// host side: tensor maps + launch
+// ------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)f;
+  });
+  return fn;
+}
+
+// 2-D map over a row-major [rows, cols] matrix of 16-bit elements, row pitch in elements; box = 64 cols x box_rows.
+static bool make_map_2d(CUtensorMap* m, const void* ptr, int dtype, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
+                        uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {pitch_elems * 2};
+  const cuuint32_t box[2] = {64, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == FA_DT_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  return fn(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, int HD, int HDV, int KST, int VST>
+static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_rows, cudaStream_t stream) {
+  using SM = Smem<HD, HDV, KST, VST>;
+  TcArgs a;
+  a.kp = kp;
+  a.max_pairs = (kp.max_seqlen_q + 2 * TM - 1) / (2 * TM);
+  a.num_items = kp.batch * kp.hq * a.max_pairs;
+  const bool paged = kp.page_table != nullptr;
+  a.kv_box_rows = paged ? (kp.page_size < TN ? kp.page_size : TN) : TN;
+  a.kv_total_rows = (int)kv_rows;
+  CUtensorMap mq, mk, mv;
+  if (!make_map_2d(&mq, kp.q, dtype, (uint64_t)kp.total_q, (uint64_t)kp.hq * HD, (uint64_t)kp.q_row_stride, TM)) return -1;
+  if (!make_map_2d(&mk, kp.k, dtype, kv_rows, (uint64_t)kp.hkv * HD, (uint64_t)kp.k_row_stride, a.kv_box_rows)) return -1;
+  if (!make_map_2d(&mv, kp.v, dtype, kv_rows, (uint64_t)kp.hkv * HDV, (uint64_t)kp.v_row_stride, a.kv_box_rows)) return -1;
+  auto kern = fwd_prefill_tc_kernel<T, HD, HDV, KST, VST>;
+  int smem = SM::kBytes + 1024;
+  if (smem < 120 * 1024) smem = 120 * 1024;   // one CTA per SM: the CTA owns all 512 TMEM columns
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return (int)e;
+  const int grid = a.num_items < pl.num_sms ? a.num_items : pl.num_sms;
+  if (grid <= 0) return 0;
+  kern<<<grid, NTHREADS, smem, stream>>>(a, mq, mk, mv);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace tc
+
+// Shapes the tensor-core prefill route takes. Layout conditions (heads back to back inside a row, pages
+// back to back) are checked at launch: fa_b200_fwd re-plans onto the general route when they do not hold.
+bool prefill_tc_supported(const PlanInput& in) {
+  if (in.q_dtype != in.kv_dtype || in.q_dtype == FA_DT_FP8_E4M3) return false;
+  const bool hd_ok = (in.hd == 64 && in.hdv == 64) || (in.hd == 128 && in.hdv == 128) || (in.hd == 192 && in.hdv == 128);
+  if (!hd_ok) return false;
+  if (in.page_size > 0) {
+    const int ps = in.page_size;
+    if (ps % 8 != 0 || !((128 % ps == 0) || (ps % 128 == 0))) return false;
+  }
+  return in.hkv > 0 && in.hq % in.hkv == 0;
+}
+
+bool prefill_tc_layout_ok(const FaFwdParams* p) {
+  if (p->q_head_stride != p->hd || p->k_head_stride != p->hd || p->v_head_stride != p->hdv) return false;
+  if (p->q_row_stride < (int64_t)p->hq * p->hd) return false;
+  if (p->page_table) {
+    if (p->k_page_stride != (int64_t)p->page_size * p->k_row_stride) return false;
+    if (p->v_page_stride != (int64_t)p->page_size * p->v_row_stride) return false;
+    if (p->num_pages <= 0) return false;
+  }
+  return true;
+}
+
+int launch_prefill_tc(const KParams& kp, const Plan& pl, int dtype, cudaStream_t stream) {
+  const uint64_t kv_rows = kp.page_table ? (uint64_t)kp.num_pages * (uint64_t)kp.page_size : (uint64_t)kp.total_k;
+  const bool bf = dtype != FA_DT_FP16;
+  if (kp.hd == 128 && kp.hdv == 128)
+    return bf ? tc::launch_impl<__nv_bfloat16, 128, 128, 2, 2>(kp, pl, dtype, kv_rows, stream)
+              : tc::launch_impl<__half, 128, 128, 2, 2>(kp, pl, dtype, kv_rows, stream);
+  if (kp.hd == 64 && kp.hdv == 64)
+    return bf ? tc::launch_impl<__nv_bfloat16, 64, 64, 3, 3>(kp, pl, dtype, kv_rows, stream)
+              : tc::launch_impl<__half, 64, 64, 3, 3>(kp, pl, dtype, kv_rows, stream);
+  if (kp.hd == 192 && kp.hdv == 128)
+    return bf ? tc::launch_impl<__nv_bfloat16, 192, 128, 2, 1>(kp, pl, dtype, kv_rows, stream)
+              : tc::launch_impl<__half, 192, 128, 2, 1>(kp, pl, dtype, kv_rows, stream);
+  return -1;
+}
+
 }  // namespace fa

@@ -41,6 +41,7 @@ struct PlanInput {
   int is_causal, window_left, window_right, has_softcap;
   int num_splits, sm_margin, route;
   int num_sms_device;
+  int tc_layout_ok;   // strides allow the 2-D TMA views the tensor-core prefill route needs
 };
 
 Plan make_plan(const PlanInput& in);

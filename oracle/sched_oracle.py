@@ -23,7 +23,7 @@ MAGIC, VERSION, HEADER, SORT_MAX = 0x46413230, 1, 16, 8192
 ROUTE_AUTO, ROUTE_PREFILL_TC, ROUTE_DECODE, ROUTE_GENERAL = 0, 1, 2, 3
 DT_BF16, DT_FP16, DT_FP8 = 0, 1, 2
 # which kernel families the library under test ships (the planner only routes to these)
-TC_ENABLED, DECODE_ENABLED = False, False
+TC_ENABLED, DECODE_ENABLED = True, False
 
 
 def cdiv(a: int, b: int) -> int:
@@ -77,7 +77,7 @@ class Plan:
 
 
 def prefill_tc_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> bool:
-    if q_dtype != kv_dtype:
+    if q_dtype != kv_dtype or q_dtype == DT_FP8:
         return False
     if (hd, hdv) not in ((64, 64), (128, 128), (192, 128)):
         return False
@@ -123,7 +123,7 @@ def make_plan(*, batch, max_seqlen_q, max_seqlen_k, hq, hkv, hd, hdv, q_dtype=DT
     heads = hkv if rpt > 1 else hq
     ctas = batch * heads * max_mtiles
     s = 1
-    if num_splits == 1:
+    if route == ROUTE_PREFILL_TC or num_splits == 1:
         s = 1
     elif num_splits > 1:
         s = min(num_splits, max_nb)

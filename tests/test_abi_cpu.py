@@ -76,6 +76,12 @@ def test_host_plan_matches_integer_oracle(case, num_splits):
         if hasattr(p, k_):
             setattr(p, k_, v_)
     p.page_table = 4096 if case["page_size"] else None
+    p.num_pages = 1024
+    # packed layouts: heads back to back inside a token row, pages back to back
+    p.q_head_stride, p.k_head_stride, p.v_head_stride = case["hd"], case["hd"], case["hdv"]
+    p.q_row_stride, p.k_row_stride = case["hq"] * case["hd"], case["hkv"] * case["hd"]
+    p.v_row_stride = case["hkv"] * case["hdv"]
+    p.k_page_stride, p.v_page_stride = case["page_size"] * p.k_row_stride, case["page_size"] * p.v_row_stride
     p.num_splits = num_splits
     p.total_q = case["batch"] * case["max_seqlen_q"]
     assert lib.fa_b200_num_splits(ctypes.byref(p)) == plan.nsplits
