@@ -204,8 +204,9 @@ def fwd(q, k, v, *, out=None, workspace=None, check=False, **kw):
 
 def num_splits(q, k, v, **kw) -> int:
     lib = load()
-    out = torch.empty(0, device=q.device, dtype=torch.bfloat16 if q.dtype == torch.float8_e4m3fn else q.dtype)
-    lse = torch.empty(0, device=q.device, dtype=torch.float32)
+    out = torch.empty(q.shape[0], q.shape[1], v.shape[-1], device=q.device,
+                      dtype=torch.bfloat16 if q.dtype == torch.float8_e4m3fn else q.dtype)
+    lse = torch.empty(q.shape[1], q.shape[0], device=q.device, dtype=torch.float32)
     p, _ = make_params(q, k, v, out, lse, **kw)
     return lib.fa_b200_num_splits(C.byref(p))
 

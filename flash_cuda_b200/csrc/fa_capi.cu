@@ -86,11 +86,11 @@ Plan make_plan(const PlanInput& in) {
   int route = in.route;
   const bool tc_ok = prefill_tc_supported(in) && in.tc_layout_ok, dec_ok = decode_supported(in);
   if (route == FA_ROUTE_AUTO) {
-    if (dec_ok && in.max_seqlen_q * rep <= 64) route = FA_ROUTE_DECODE;
+    if (dec_ok && in.max_seqlen_q * rep <= 16) route = FA_ROUTE_DECODE;
     else if (tc_ok) route = FA_ROUTE_PREFILL_TC;
     else route = FA_ROUTE_GENERAL;
   }
-  if ((route == FA_ROUTE_PREFILL_TC && !tc_ok) || (route == FA_ROUTE_DECODE && !dec_ok)) {
+  if ((route == FA_ROUTE_PREFILL_TC && !tc_ok) || (route == FA_ROUTE_DECODE && !(dec_ok && in.max_seqlen_q * rep <= 16))) {
     pl.err = FA_ERR_UNSUPPORTED;
     return pl;
   }
@@ -98,7 +98,7 @@ Plan make_plan(const PlanInput& in) {
   if (route == FA_ROUTE_PREFILL_TC) {
     pl.tile_m = 256; pl.tile_n = 128; pl.rows_per_token = 1;
   } else if (route == FA_ROUTE_DECODE) {
-    pl.tile_m = 64; pl.tile_n = 64; pl.rows_per_token = rep;
+    pl.tile_m = 16; pl.tile_n = 64; pl.rows_per_token = rep;
   } else {
     if (in.hd > 256 || in.hdv > 256 || in.hd % 8 != 0 || in.hdv % 8 != 0) { pl.err = FA_ERR_UNSUPPORTED; return pl; }
     pl.tile_m = 64; pl.tile_n = 64; pl.rows_per_token = rep;

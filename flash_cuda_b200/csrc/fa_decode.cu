@@ -1,7 +1,552 @@
-// placeholder until the paged-decode kernel lands
+// fa_decode.cu — paged-KV decode: a bandwidth-bound streaming kernel.
+//
+// Work item = (batch entry, kv head, split).  The `rep * q_len <= 16` query rows that share one KV head are
+// packed into one 16-row MMA tile, so every K/V byte is read from HBM once per kv head.  Persistent CTAs
+// (one per SM) pull work items longest-first from the scheduler metadata through an atomic counter.
+//
+//   warp 4      producer: resolves page-table entries (32 at a time, one coalesced load) and streams whole
+//               pages with TMA 2-D boxes over the page pool viewed as [num_pages * page_size, hkv * hd] into a
+//               ring of 64-key stages (K 16 KB + V 16 KB each, 128-byte swizzle).  The ring runs on across
+//               work-item boundaries; each stage carries a small descriptor (work id, first key, flags).
+//   warps 0-3   consumers: each takes 16 of the stage's 64 keys: S = Q K^T and O += P V with warp-level
+//               MMA (ldmatrix from the swizzled stage), a private online softmax, and at the end of the work
+//               item a cross-warp merge through shared memory.
+// The tensor cores are incidental here: the roofline is HBM, the design goal is bytes in flight.
+//
+// Plays the role of `fwd_kernel_ws_paged` + `launch_ws_paged` of the reference
+// (kernels/fa4_blackwell.cu:8774-9103, 9605-9993), with per-batch leftpad and fp8 KV (descale folded in).
+#include <cuda.h>
+
+#include <mutex>
+
 #include "fa_internal.h"
 #include "fa_sched.h"
+#include "ptx.cuh"
+
 namespace fa {
-bool decode_supported(const PlanInput&) { return false; }
-int launch_decode(const KParams&, const Plan&, int, cudaStream_t) { return -1; }
+namespace dec {
+
+constexpr int TN = 64;                 // keys per stage
+constexpr int NCONS = 4;               // consumer warps
+constexpr int NTHREADS = (NCONS + 1) * 32;
+constexpr int HD = 128, HDV = 128;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+enum Role : unsigned { ROLE_PRODUCER = 5, ROLE_CONSUMER = 6 };
+enum : int { F_FIRST = 1, F_LAST = 2, F_EMPTY = 4 };
+
+struct DecArgs {
+  KParams kp;
+  int total_work;     // num_work * hkv * nsplits
+  int box_rows;       // rows per TMA box = min(page_size, 64)
+  int kv_total_rows;
+};
+
+template <int ESZ, int NST>
+struct Smem {
+  static constexpr int kKBytes = TN * HD * ESZ, kVBytes = TN * HDV * ESZ;
+  static constexpr int kStage = kKBytes + kVBytes;
+  static constexpr int kRing = NST * kStage;
+  static constexpr int kInfoOff = kRing;                       // NST x int4
+  static constexpr int kBarOff = kInfoOff + NST * 16;          // full[NST], empty[NST]
+  static constexpr int kMiscOff = kBarOff + 2 * NST * 8;       // abort flags
+  static constexpr int kScrOff = (kMiscOff + 16 + 15) / 16 * 16;
+  static constexpr int kLdO = HDV + 4;
+  static constexpr int kScrBytes = NCONS * 16 * kLdO * 4 + 2 * NCONS * 16 * 4;
+  static constexpr int kBytes = kScrOff + kScrBytes;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  unsigned long long t0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+#pragma unroll 1
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    unsigned long long t1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
+    if (t1 - t0 > 2000000000ull) return false;
+  }
+}
+
+__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(NCONS * 32) : "memory"); }
+
+struct WorkItem {
+  int b, hk, split, lo, hi;   // key-block range [lo, hi) in units of TN keys
+  int seqlen_q, seqlen_k, q0, leftpad;
+  bool valid;
+};
+
+__device__ __forceinline__ WorkItem decode_work(const KParams& p, int w) {
+  WorkItem it;
+  const int per_entry = p.hkv * p.nsplits;
+  const int e = w / per_entry, rem = w - e * per_entry;
+  it.hk = rem / p.nsplits;
+  it.split = rem - it.hk * p.nsplits;
+  const int32_t* ent = p.work + kSchedHeader + 4 * e;
+  it.b = ent[0];
+  it.valid = it.b >= 0;
+  it.lo = it.hi = 0;
+  it.seqlen_q = it.seqlen_k = it.q0 = it.leftpad = 0;
+  if (it.valid) {
+    split_range(ent[2], ent[3], it.split, p.nsplits, &it.lo, &it.hi);
+    it.q0 = p.cu_q[it.b];
+    it.seqlen_q = p.cu_q[it.b + 1] - it.q0;
+    it.seqlen_k = p.seqused_k[it.b];
+    it.leftpad = p.leftpad_k ? p.leftpad_k[it.b] : 0;
+  }
+  return it;
+}
+
+// T = MMA element type (bf16 / fp16); KV8 = the cache holds e4m3 bytes.
+template <typename T, bool KV8, int NST>
+__global__ void __launch_bounds__(NTHREADS, 1)
+fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+  constexpr int ESZ = KV8 ? 1 : 2;
+  using SM = Smem<ESZ, NST>;
+  const KParams& p = a.kp;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t raw = smem_u32(smem_dyn);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* sm = smem_dyn + (base - raw);
+  const uint32_t bar_full = base + SM::kBarOff, bar_empty = bar_full + 8 * NST;
+  volatile int* s_info = reinterpret_cast<volatile int*>(sm + SM::kInfoOff);   // 4 ints per stage
+  volatile int* s_abort = reinterpret_cast<volatile int*>(sm + SM::kMiscOff);
+  float* s_o = reinterpret_cast<float*>(sm + SM::kScrOff);
+  float* s_m = s_o + NCONS * 16 * SM::kLdO;
+  float* s_l = s_m + NCONS * 16;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    for (int s = 0; s < NST; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, NCONS); }
+    s_abort[0] = 0; s_abort[1] = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == NCONS) {
+    // ============================================ producer ============================================
+    if (lane == 0) { tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); }
+    uint32_t cnt = 0;
+    bool ok = true;
+    const int ps = p.page_size;
+    const int boxes = TN / a.box_rows;          // TMA boxes per stage and 128-byte column block
+    while (ok) {
+      int w = 0;
+      if (lane == 0) w = atomicAdd(p.counters, 1);
+      w = __shfl_sync(0xffffffffu, w, 0);
+      if (w >= a.total_work) break;
+      const WorkItem it = decode_work(p, w);
+      if (!it.valid) continue;
+      if (it.lo >= it.hi) {   // nothing to stream: one descriptor-only stage so that the output still gets written
+        const uint32_t s = cnt % NST;
+        ok = wait_or_abort(bar_empty + 8 * s, ((cnt / NST) & 1) ^ 1, s_abort);
+        if (!ok) break;
+        if (lane == 0) {
+          s_info[4 * s] = w; s_info[4 * s + 1] = 0; s_info[4 * s + 2] = F_FIRST | F_LAST | F_EMPTY;
+          mbar_arrive(bar_full + 8 * s);
+        }
+        ++cnt;
+        continue;
+      }
+      const int npages = (it.seqlen_k + ps - 1) / ps;
+      int cache_first = -1, cache_id = 0;       // 32 page-table entries, one per lane
+      for (int nb = it.lo; nb < it.hi && ok; ++nb) {
+        const int key0 = nb * TN;
+        const int lp0 = key0 / ps;              // first logical page of this stage
+        if (cache_first < 0 || lp0 < cache_first || lp0 + boxes > cache_first + 32) {
+          cache_first = lp0;
+          const int lp = lp0 + lane;
+          cache_id = lp < npages ? p.page_table[(int64_t)it.b * p.page_table_stride + lp] : -1;
+        }
+        const uint32_t s = cnt % NST;
+        ok = wait_or_abort(bar_empty + 8 * s, ((cnt / NST) & 1) ^ 1, s_abort);
+        if (!ok) break;
+        const uint32_t kdst = base + s * SM::kStage, vdst = kdst + SM::kKBytes;
+        if (lane == 0) {
+          int flags = 0;
+          if (nb == it.lo) flags |= F_FIRST;
+          if (nb + 1 == it.hi) flags |= F_LAST;
+          s_info[4 * s] = w; s_info[4 * s + 1] = key0; s_info[4 * s + 2] = flags;
+          mbar_expect_tx(bar_full + 8 * s, SM::kStage);
+        }
+        for (int j = 0; j < boxes; ++j) {
+          const int kk = key0 + j * a.box_rows;
+          const int lp = kk / ps;
+          const int pid = __shfl_sync(0xffffffffu, cache_id, lp - cache_first);
+          if (lane == 0) {
+            const int y = (kk < it.seqlen_k && pid >= 0) ? pid * ps + (kk - lp * ps) : a.kv_total_rows;
+            const uint32_t roff = (uint32_t)(j * a.box_rows) * 128u;
+            if (KV8) {
+              tma_load_2d(kdst + roff, &map_k, it.hk * HD, y, bar_full + 8 * s);
+              tma_load_2d(vdst + roff, &map_v, it.hk * HDV, y, bar_full + 8 * s);
+            } else {
+#pragma unroll
+              for (int cb = 0; cb < 2; ++cb) {
+                tma_load_2d(kdst + cb * (TN * 128) + roff, &map_k, it.hk * HD + cb * 64, y, bar_full + 8 * s);
+                tma_load_2d(vdst + cb * (TN * 128) + roff, &map_v, it.hk * HDV + cb * 64, y, bar_full + 8 * s);
+              }
+            }
+          }
+        }
+        ++cnt;
+      }
+    }
+    if (!ok) { if (lane == 0) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_PRODUCER); s_abort[0] = 1; } }
+    if (ok) {   // end-of-stream marker
+      const uint32_t s = cnt % NST;
+      if (wait_or_abort(bar_empty + 8 * s, ((cnt / NST) & 1) ^ 1, s_abort)) {
+        if (lane == 0) { s_info[4 * s] = -1; mbar_arrive(bar_full + 8 * s); }
+        ++cnt;
+      }
+    }
+    // every copy issued must have landed before the CTA may leave
+    if (lane == 0) {
+      for (uint32_t s = 0; s < (uint32_t)NST; ++s)
+        if (cnt > s) wait_or_abort(bar_full + 8 * s, ((cnt - 1 - s) / NST) & 1, s_abort + 1);
+    }
+  } else {
+    // ============================================ consumers ===========================================
+    const int g = lane >> 2, tq = lane & 3;
+    const int rep = p.rep;
+    uint32_t cnt = 0;
+    bool ok = true;
+    uint32_t qf[HD / 16][4];
+    float o[HDV / 8][4];
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    int lo_a = 0, hi_a = -1, lo_b = 0, hi_b = -1, lo_max = 0, hi_min = -1;
+    float c_mul = 0.f, cap_in = 0.f, vds = 1.f;
+    WorkItem it{};
+    const bool has_cap = p.softcap > 0.f;
+
+    while (true) {
+      const uint32_t s = cnt % NST;
+      ok = wait_or_abort(bar_full + 8 * s, (cnt / NST) & 1, s_abort);
+      if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_CONSUMER); s_abort[0] = 1; break; }
+      const int4 info = make_int4(s_info[4 * s], s_info[4 * s + 1], s_info[4 * s + 2], 0);
+      if (info.x < 0) break;
+      const int key0 = info.y, flags = info.z;
+      if (flags & F_FIRST) {
+        it = decode_work(p, info.x);
+        const int rows_total = it.seqlen_q * rep;
+        // Q fragments straight from global memory (A operand of m16n8k16; rows g and g+8)
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int R = g + (e & 1) * 8;
+            // 16-bit KV: columns ks*16 + 2*tq (+8); fp8 KV: the contraction index is permuted to match the
+            // byte order ldmatrix delivers (see k_fragment): columns (ks>>1)*32 + (ks&1)*16 + 4*tq + 2*(e>>1)
+            const int c = KV8 ? ((ks >> 1) * 32 + (ks & 1) * 16 + 4 * tq + 2 * (e >> 1)) : (ks * 16 + 2 * tq + (e >> 1) * 8);
+            uint32_t v = 0;
+            if (R < rows_total) {
+              const int token = R / rep, head = it.hk * rep + R % rep;
+              v = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(p.q) +
+                                                     (int64_t)(it.q0 + token) * p.q_row_stride +
+                                                     (int64_t)head * p.q_head_stride + c);
+            }
+            qf[ks][e] = v;
+          }
+        }
+        float sc = p.scale;
+        vds = 1.f;
+        const int di = it.b * p.descale_batch_stride + it.hk * p.descale_head_stride;
+        if (p.k_descale) sc *= p.k_descale[di];
+        if (p.v_descale) vds = p.v_descale[di];
+        c_mul = has_cap ? p.softcap * kLog2e : sc * kLog2e;
+        cap_in = has_cap ? sc / p.softcap : 0.f;
+        const int off = it.seqlen_k - it.seqlen_q;
+        const int qp_a = off + g / rep, qp_b = off + (g + 8) / rep;
+        lo_a = lo_b = it.leftpad;
+        hi_a = hi_b = it.seqlen_k - 1;
+        if (p.is_causal) { hi_a = min(hi_a, qp_a); hi_b = min(hi_b, qp_b); }
+        if (p.window_right >= 0) { hi_a = min(hi_a, qp_a + p.window_right); hi_b = min(hi_b, qp_b + p.window_right); }
+        if (p.window_left >= 0) { lo_a = max(lo_a, qp_a - p.window_left); lo_b = max(lo_b, qp_b - p.window_left); }
+        // bounds valid for all 16 rows (rows past rows_total included: conservative)
+        const int qp_lo = off, qp_hi = off + 15 / rep;
+        lo_max = it.leftpad; hi_min = it.seqlen_k - 1;
+        if (p.is_causal) hi_min = min(hi_min, qp_lo);
+        if (p.window_right >= 0) hi_min = min(hi_min, qp_lo + p.window_right);
+        if (p.window_left >= 0) lo_max = max(lo_max, qp_hi - p.window_left);
+        m_a = m_b = -INFINITY; l_a = l_b = 0.f;
+#pragma unroll
+        for (int i = 0; i < HDV / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+      }
+
+      if (!(flags & F_EMPTY)) {
+        const uint32_t kb = base + s * SM::kStage, vb = kb + SM::kKBytes;
+        const int mat = lane >> 3, l7 = lane & 7;
+        float sacc[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) { sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f; }
+        if (!KV8) {
+          const uint32_t krow = kb + (uint32_t)(warp * 16 + (mat >> 1) * 8 + l7) * 128u;
+#pragma unroll
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            uint32_t bfr[4];
+            const uint32_t chunk = (uint32_t)((ks * 2 + (mat & 1)) & 7);
+            ldmatrix_x4(bfr, krow + (ks >> 2) * (TN * 128) + ((chunk ^ (uint32_t)l7) << 4));
+            mma_16816<T>(sacc[0], qf[ks], bfr[0], bfr[1]);
+            mma_16816<T>(sacc[1], qf[ks], bfr[2], bfr[3]);
+          }
+        } else {
+          // fp8 rows are 128 bytes: one swizzle row per key.  ldmatrix moves 16-byte chunks, so a lane ends up
+          // with 4 consecutive e4m3 values of key (lane/4); they are widened in registers and fed to the
+          // 16-bit MMA with the contraction index permuted consistently on the Q side.
+          const uint32_t krow = kb + (uint32_t)(warp * 16 + (mat >> 1) * 8 + l7) * 128u;
+#pragma unroll
+          for (int k32 = 0; k32 < HD / 32; ++k32) {
+            uint32_t raw4[4];
+            const uint32_t chunk = (uint32_t)(k32 * 2 + (mat & 1));
+            ldmatrix_x4(raw4, krow + ((chunk ^ (uint32_t)l7) << 4));
+            uint32_t b00, b01, b10, b11, b20, b21, b30, b31;
+            e4m3x4_to<T>(raw4[0], b00, b01);   // keys 0-7, bytes 32*k32 + 4tq .. +3
+            e4m3x4_to<T>(raw4[1], b10, b11);   // keys 0-7, bytes 32*k32 + 16 + 4tq .. +3
+            e4m3x4_to<T>(raw4[2], b20, b21);   // keys 8-15
+            e4m3x4_to<T>(raw4[3], b30, b31);
+            mma_16816<T>(sacc[0], qf[2 * k32], b00, b01);
+            mma_16816<T>(sacc[0], qf[2 * k32 + 1], b10, b11);
+            mma_16816<T>(sacc[1], qf[2 * k32], b20, b21);
+            mma_16816<T>(sacc[1], qf[2 * k32 + 1], b30, b31);
+          }
+        }
+        // ---- mask + online softmax over this warp's 16 keys ----
+        const int kbase = key0 + warp * 16;
+        const bool full = (kbase >= lo_max) && (kbase + 15 <= hi_min);
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float y = sacc[nt][e];
+            y = has_cap ? tanh_fast(y * cap_in) * c_mul : y * c_mul;
+            if (!full) {
+              const int kk = kbase + nt * 8 + 2 * tq + (e & 1);
+              const bool okk = e >= 2 ? (kk >= lo_b && kk <= hi_b) : (kk >= lo_a && kk <= hi_a);
+              y = okk ? y : -INFINITY;
+            }
+            sacc[nt][e] = y;
+            if (e >= 2) mx_b = fmaxf(mx_b, y); else mx_a = fmaxf(mx_a, y);
+          }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float ms_a = mn_a == -INFINITY ? 0.f : mn_a, ms_b = mn_b == -INFINITY ? 0.f : mn_b;
+        const float corr_a = ex2(m_a - ms_a), corr_b = ex2(m_b - ms_b);
+        m_a = mn_a; m_b = mn_b;
+        float ps_a = 0.f, ps_b = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+          sacc[nt][0] = ex2(sacc[nt][0] - ms_a); sacc[nt][1] = ex2(sacc[nt][1] - ms_a);
+          sacc[nt][2] = ex2(sacc[nt][2] - ms_b); sacc[nt][3] = ex2(sacc[nt][3] - ms_b);
+          ps_a += sacc[nt][0] + sacc[nt][1];
+          ps_b += sacc[nt][2] + sacc[nt][3];
+        }
+        l_a = l_a * corr_a + ps_a;
+        l_b = l_b * corr_b + ps_b;
+        if (__any_sync(0xffffffffu, corr_a != 1.f || corr_b != 1.f)) {
+#pragma unroll
+          for (int i = 0; i < HDV / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
+        }
+        uint32_t pa[4];
+        pa[0] = pack2<T>(sacc[0][0], sacc[0][1]);
+        pa[1] = pack2<T>(sacc[0][2], sacc[0][3]);
+        pa[2] = pack2<T>(sacc[1][0], sacc[1][1]);
+        pa[3] = pack2<T>(sacc[1][2], sacc[1][3]);
+        // ---- O += P V ----
+        if (!KV8) {
+          const uint32_t vrow = vb + (uint32_t)(warp * 16 + (mat & 1) * 8 + l7) * 128u;
+#pragma unroll
+          for (int np = 0; np < HDV / 16; ++np) {
+            uint32_t bfr[4];
+            const uint32_t chunk = (uint32_t)((np * 2 + (mat >> 1)) & 7);
+            ldmatrix_x4_trans(bfr, vrow + (np >> 2) * (TN * 128) + ((chunk ^ (uint32_t)l7) << 4));
+            mma_16816<T>(o[2 * np], pa, bfr[0], bfr[1]);
+            mma_16816<T>(o[2 * np + 1], pa, bfr[2], bfr[3]);
+          }
+        } else {
+          // fp8 V: the B fragment needs pairs of KEYS for one value column, i.e. bytes of different rows.
+          // Gather them with byte loads: keys {2tq, 2tq+1, 2tq+8, 2tq+9} of this warp's 16, column g + 8*nt.
+          const uint32_t r0 = (uint32_t)(warp * 16 + 2 * tq);
+#pragma unroll
+          for (int nt = 0; nt < HDV / 8; ++nt) {
+            const uint32_t col = (uint32_t)(nt * 8 + g);
+            uint32_t by[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t r = r0 + (j & 1) + (j >> 1) * 8;
+              const uint32_t addr = vb + r * 128u + ((((col >> 4) ^ (r & 7u)) << 4) | (col & 15u));
+              asm volatile("ld.shared.u8 %0, [%1];" : "=r"(by[j]) : "r"(addr));
+            }
+            uint32_t b0, b1;
+            e4m3x4_to<T>(by[0] | (by[1] << 8) | (by[2] << 16) | (by[3] << 24), b0, b1);
+            mma_16816<T>(o[nt], pa, b0, b1);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+      ++cnt;
+
+      if (flags & F_LAST) {
+        // ---- merge the four warps' partial results and write the output rows ----
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        float* so = s_o + warp * 16 * SM::kLdO;
+#pragma unroll
+        for (int nt = 0; nt < HDV / 8; ++nt) {
+          *reinterpret_cast<float2*>(so + g * SM::kLdO + nt * 8 + 2 * tq) = make_float2(o[nt][0], o[nt][1]);
+          *reinterpret_cast<float2*>(so + (g + 8) * SM::kLdO + nt * 8 + 2 * tq) = make_float2(o[nt][2], o[nt][3]);
+        }
+        if (tq == 0) {
+          s_m[warp * 16 + g] = m_a; s_m[warp * 16 + g + 8] = m_b;
+          s_l[warp * 16 + g] = l_a; s_l[warp * 16 + g + 8] = l_b;
+        }
+        bar_consumers();
+        {
+          const int R = tid >> 3, c0 = (tid & 7) * 16;
+          const int rows_total = it.seqlen_q * rep;
+          float mw[NCONS], M = -INFINITY;
+#pragma unroll
+          for (int wi = 0; wi < NCONS; ++wi) { mw[wi] = s_m[wi * 16 + R]; M = fmaxf(M, mw[wi]); }
+          float L = 0.f, acc[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+#pragma unroll
+          for (int wi = 0; wi < NCONS; ++wi) {
+            const float e = mw[wi] == -INFINITY ? 0.f : ex2(mw[wi] - M);
+            L += e * s_l[wi * 16 + R];
+            const float* src = s_o + (wi * 16 + R) * SM::kLdO + c0;
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+              const float4 v4 = *reinterpret_cast<const float4*>(src + j);
+              acc[j] += e * v4.x; acc[j + 1] += e * v4.y; acc[j + 2] += e * v4.z; acc[j + 3] += e * v4.w;
+            }
+          }
+          if (R < rows_total) {
+            const int token = R / rep, head = it.hk * rep + R % rep;
+            const int64_t qi = it.q0 + token;
+            if (p.nsplits > 1) {
+              const float inv = L > 0.f ? vds / L : 0.f;
+              float* op = p.o_part + (((int64_t)it.split * p.total_q + qi) * p.hq + head) * p.hdv + c0;
+#pragma unroll
+              for (int j = 0; j < 16; j += 4)
+                *reinterpret_cast<float4*>(op + j) = make_float4(acc[j] * inv, acc[j + 1] * inv, acc[j + 2] * inv, acc[j + 3] * inv);
+              if ((tid & 7) == 0)
+                p.lse_part[((int64_t)it.split * p.hq + head) * p.total_q + qi] = L > 0.f ? (M + lg2(L)) * kLn2 : -INFINITY;
+            } else {
+              float osc = 1.f;
+              if (p.s_aux) {
+                const float ys = p.s_aux[head] * kLog2e;
+                const float mn = fmaxf(M, ys);
+                osc = M == -INFINITY ? 0.f : ex2(M - mn);
+                L = L * osc + ex2(ys - mn);
+                M = mn;
+              }
+              const float inv = L > 0.f ? osc * vds / L : 0.f;
+              T* op = reinterpret_cast<T*>(p.out) + qi * p.o_row_stride + (int64_t)head * p.o_head_stride + c0;
+              uint4 v0, v1;
+              v0.x = pack2<T>(acc[0] * inv, acc[1] * inv);   v0.y = pack2<T>(acc[2] * inv, acc[3] * inv);
+              v0.z = pack2<T>(acc[4] * inv, acc[5] * inv);   v0.w = pack2<T>(acc[6] * inv, acc[7] * inv);
+              v1.x = pack2<T>(acc[8] * inv, acc[9] * inv);   v1.y = pack2<T>(acc[10] * inv, acc[11] * inv);
+              v1.z = pack2<T>(acc[12] * inv, acc[13] * inv); v1.w = pack2<T>(acc[14] * inv, acc[15] * inv);
+              *reinterpret_cast<uint4*>(op) = v0;
+              *reinterpret_cast<uint4*>(op + 8) = v1;
+              if ((tid & 7) == 0) p.lse[(int64_t)head * p.total_q + qi] = L > 0.f ? (M + lg2(L)) * kLn2 : -INFINITY;
+            }
+          }
+        }
+        bar_consumers();   // the scratch area is free again
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)f;
+  });
+  return fn;
+}
+
+// [rows, cols] row-major, 128-byte wide boxes of box_rows rows, 128-byte swizzle
+static bool make_map(CUtensorMap* m, const void* ptr, int dtype, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
+                     uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  const uint32_t esz = dtype == FA_DT_FP8_E4M3 ? 1 : 2;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {pitch_elems * esz};
+  const cuuint32_t box[2] = {128 / esz, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = dtype == FA_DT_FP8_E4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : dtype == FA_DT_FP16   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                         : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  return fn(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename T, bool KV8, int NST>
+static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaStream_t stream) {
+  using SM = Smem<KV8 ? 1 : 2, NST>;
+  DecArgs a;
+  a.kp = kp;
+  a.total_work = num_work_slots * kp.hkv * kp.nsplits;
+  a.box_rows = kp.page_size < TN ? kp.page_size : TN;
+  const uint64_t rows = (uint64_t)kp.num_pages * (uint64_t)kp.page_size;
+  a.kv_total_rows = (int)rows;
+  const int kvdt = KV8 ? FA_DT_FP8_E4M3 : (std::is_same<T, __half>::value ? FA_DT_FP16 : FA_DT_BF16);
+  CUtensorMap mk, mv;
+  if (!make_map(&mk, kp.k, kvdt, rows, (uint64_t)kp.hkv * HD, (uint64_t)kp.k_row_stride, a.box_rows)) return -1;
+  if (!make_map(&mv, kp.v, kvdt, rows, (uint64_t)kp.hkv * HDV, (uint64_t)kp.v_row_stride, a.box_rows)) return -1;
+  auto kern = fwd_decode_kernel<T, KV8, NST>;
+  const int smem = SM::kBytes + 1024;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return (int)e;
+  int grid = a.total_work < pl.num_sms ? a.total_work : pl.num_sms;
+  if (grid <= 0) return 0;
+  kern<<<grid, NTHREADS, smem, stream>>>(a, mk, mv);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace dec
+
+// Shapes the decode route takes: paged KV, head_dim 128, 16-bit queries, page sizes that are whole TMA boxes.
+bool decode_supported(const PlanInput& in) {
+  if (in.q_dtype == FA_DT_FP8_E4M3) return false;
+  if (in.kv_dtype != in.q_dtype && in.kv_dtype != FA_DT_FP8_E4M3) return false;
+  if (in.hd != 128 || in.hdv != 128) return false;
+  const int ps = in.page_size;
+  if (!(ps == 16 || ps == 32 || ps == 64 || ps == 128)) return false;
+  return in.hkv > 0 && in.hq % in.hkv == 0 && in.tc_layout_ok;
+}
+
+int launch_decode(const KParams& kp, const Plan& pl, int compute_dtype, cudaStream_t stream) {
+  // every (batch, m_tile) slot of the metadata may hold a work entry; m_tile is always 0 on this route
+  const int slots = kp.batch * pl.max_mtiles;
+  const bool bf = compute_dtype != FA_DT_FP16;
+  if (kp.kv_fp8)
+    return bf ? dec::launch_t<__nv_bfloat16, true, 10>(kp, pl, slots, stream)
+              : dec::launch_t<__half, true, 10>(kp, pl, slots, stream);
+  return bf ? dec::launch_t<__nv_bfloat16, false, 5>(kp, pl, slots, stream)
+            : dec::launch_t<__half, false, 5>(kp, pl, slots, stream);
+}
+
 }  // namespace fa

@@ -413,10 +413,18 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
               if (col < rlo || col > rhi) sreg[c][j] = 0xff800000u;   // -inf
             }
         }
+        {
+          // eight independent chains instead of one 128-deep dependency chain
+          float mxa[8];
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+          for (int j = 0; j < 8; ++j) mxa[j] = __uint_as_float(sreg[0][j]);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, __uint_as_float(sreg[c][j]));
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int j = (c == 0 ? 8 : 0); j < 32; ++j) mxa[j & 7] = fmaxf(mxa[j & 7], __uint_as_float(sreg[c][j]));
+          mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
+                     fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
+        }
         const float y_max = mx * c_mul;               // c_mul > 0, so the maximum commutes with the scale
         float corr = 1.f;
         bool rescale = false;
@@ -429,20 +437,25 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           rescale = true;
         }
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-        float psum = 0.f;
+        float2 psum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+        const float2 c2 = make_float2(c_mul, c_mul), nm2 = make_float2(neg_m, neg_m);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t pk[16];
 #pragma unroll
           for (int j = 0; j < 32; j += 2) {
-            const float p0 = ex2(fmaf(__uint_as_float(sreg[c][j]), c_mul, neg_m));
-            const float p1 = ex2(fmaf(__uint_as_float(sreg[c][j + 1]), c_mul, neg_m));
-            psum += p0 + p1;
-            pk[j >> 1] = pack2<T>(p0, p1);
+            const float2 y = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
+            const float2 pp = make_float2(ex2(y.x), ex2(y.y));
+            psum[(j >> 1) & 3] = fadd2(psum[(j >> 1) & 3], pp);
+            pk[j >> 1] = pack2<T>(pp.x, pp.y);
           }
           tmem_st16(tS + c * 16, pk);
         }
-        l += psum;
+        {
+          const float2 s01 = fadd2(psum[0], psum[1]), s23 = fadd2(psum[2], psum[3]);
+          const float2 s4 = fadd2(s01, s23);
+          l += s4.x + s4.y;
+        }
         if (__any_sync(0xffffffffu, rescale)) {
           // O_t of the previous blocks is complete: the commit behind s_full also covered PV_t(i-1)
 #pragma unroll 1

@@ -23,7 +23,7 @@ MAGIC, VERSION, HEADER, SORT_MAX = 0x46413230, 1, 16, 8192
 ROUTE_AUTO, ROUTE_PREFILL_TC, ROUTE_DECODE, ROUTE_GENERAL = 0, 1, 2, 3
 DT_BF16, DT_FP16, DT_FP8 = 0, 1, 2
 # which kernel families the library under test ships (the planner only routes to these)
-TC_ENABLED, DECODE_ENABLED = True, False
+TC_ENABLED, DECODE_ENABLED = True, True
 
 
 def cdiv(a: int, b: int) -> int:
@@ -87,7 +87,7 @@ def prefill_tc_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> b
 
 
 def decode_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> bool:
-    if q_dtype == DT_FP8:
+    if q_dtype == DT_FP8 or (kv_dtype != q_dtype and kv_dtype != DT_FP8):
         return False
     if (hd, hdv) != (128, 128):
         return False
@@ -108,7 +108,7 @@ def make_plan(*, batch, max_seqlen_q, max_seqlen_k, hq, hkv, hd, hdv, q_dtype=DT
     tc_ok = tc_enabled and prefill_tc_supported(**shape)
     dec_ok = decode_enabled and decode_supported(**shape)
     if route == ROUTE_AUTO:
-        if dec_ok and max_seqlen_q * rep <= 64:
+        if dec_ok and max_seqlen_q * rep <= 16:
             route = ROUTE_DECODE
         elif tc_ok:
             route = ROUTE_PREFILL_TC
@@ -116,6 +116,8 @@ def make_plan(*, batch, max_seqlen_q, max_seqlen_k, hq, hkv, hd, hdv, q_dtype=DT
             route = ROUTE_GENERAL
     if route == ROUTE_PREFILL_TC:
         tile_m, tile_n, rpt = 256, 128, 1
+    elif route == ROUTE_DECODE:
+        tile_m, tile_n, rpt = 16, 64, rep
     else:
         tile_m, tile_n, rpt = 64, 64, rep
     max_mtiles = cdiv(max_seqlen_q * rpt, tile_m)

@@ -12,7 +12,8 @@ from oracle.ref_attention import ref_attention
 pytestmark = pytest.mark.gpu
 
 TOL = {torch.bfloat16: 2e-2, torch.float16: 2e-2, torch.float8_e4m3fn: 6e-2}
-ROUTES = {"auto": capi.FA_ROUTE_AUTO, "general": capi.FA_ROUTE_GENERAL, "tc": capi.FA_ROUTE_PREFILL_TC}
+ROUTES = {"auto": capi.FA_ROUTE_AUTO, "general": capi.FA_ROUTE_GENERAL, "tc": capi.FA_ROUTE_PREFILL_TC,
+          "decode": capi.FA_ROUTE_DECODE}
 
 
 def _tol(q, k):
