@@ -107,6 +107,8 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   constexpr int ESZ = KV8 ? 1 : 2;
   using SM = Smem<ESZ, NST>;
+  // MMA element type: an fp8 cache is widened to fp16 (exact) and Q / P are taken to fp16 with it
+  using TM = typename std::conditional<KV8, __half, T>::type;
   const KParams& p = a.kp;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
@@ -247,6 +249,10 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
               v = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(p.q) +
                                                      (int64_t)(it.q0 + token) * p.q_row_stride +
                                                      (int64_t)head * p.q_head_stride + c);
+              if (KV8 && std::is_same<T, __nv_bfloat16>::value) {   // bf16 -> fp16, clamped to the fp16 range
+                const float lo16 = __uint_as_float(v << 16), hi16 = __uint_as_float(v & 0xffff0000u);
+                v = pack2<__half>(fminf(fmaxf(lo16, -65504.f), 65504.f), fminf(fmaxf(hi16, -65504.f), 65504.f));
+              }
             }
             qf[ks][e] = v;
           }
@@ -289,8 +295,8 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
             uint32_t bfr[4];
             const uint32_t chunk = (uint32_t)((ks * 2 + (mat & 1)) & 7);
             ldmatrix_x4(bfr, krow + (ks >> 2) * (TN * 128) + ((chunk ^ (uint32_t)l7) << 4));
-            mma_16816<T>(sacc[0], qf[ks], bfr[0], bfr[1]);
-            mma_16816<T>(sacc[1], qf[ks], bfr[2], bfr[3]);
+            mma_16816<TM>(sacc[0], qf[ks], bfr[0], bfr[1]);
+            mma_16816<TM>(sacc[1], qf[ks], bfr[2], bfr[3]);
           }
         } else {
           // fp8 rows are 128 bytes: one swizzle row per key.  ldmatrix moves 16-byte chunks, so a lane ends up
@@ -303,14 +309,14 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
             const uint32_t chunk = (uint32_t)(k32 * 2 + (mat & 1));
             ldmatrix_x4(raw4, krow + ((chunk ^ (uint32_t)l7) << 4));
             uint32_t b00, b01, b10, b11, b20, b21, b30, b31;
-            e4m3x4_to<T>(raw4[0], b00, b01);   // keys 0-7, bytes 32*k32 + 4tq .. +3
-            e4m3x4_to<T>(raw4[1], b10, b11);   // keys 0-7, bytes 32*k32 + 16 + 4tq .. +3
-            e4m3x4_to<T>(raw4[2], b20, b21);   // keys 8-15
-            e4m3x4_to<T>(raw4[3], b30, b31);
-            mma_16816<T>(sacc[0], qf[2 * k32], b00, b01);
-            mma_16816<T>(sacc[0], qf[2 * k32 + 1], b10, b11);
-            mma_16816<T>(sacc[1], qf[2 * k32], b20, b21);
-            mma_16816<T>(sacc[1], qf[2 * k32 + 1], b30, b31);
+            e4m3x4_to<TM>(raw4[0], b00, b01);   // keys 0-7, bytes 32*k32 + 4tq .. +3
+            e4m3x4_to<TM>(raw4[1], b10, b11);   // keys 0-7, bytes 32*k32 + 16 + 4tq .. +3
+            e4m3x4_to<TM>(raw4[2], b20, b21);   // keys 8-15
+            e4m3x4_to<TM>(raw4[3], b30, b31);
+            mma_16816<TM>(sacc[0], qf[2 * k32], b00, b01);
+            mma_16816<TM>(sacc[0], qf[2 * k32 + 1], b10, b11);
+            mma_16816<TM>(sacc[1], qf[2 * k32], b20, b21);
+            mma_16816<TM>(sacc[1], qf[2 * k32 + 1], b30, b31);
           }
         }
         // ---- mask + online softmax over this warp's 16 keys ----
@@ -354,10 +360,10 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
           for (int i = 0; i < HDV / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
         }
         uint32_t pa[4];
-        pa[0] = pack2<T>(sacc[0][0], sacc[0][1]);
-        pa[1] = pack2<T>(sacc[0][2], sacc[0][3]);
-        pa[2] = pack2<T>(sacc[1][0], sacc[1][1]);
-        pa[3] = pack2<T>(sacc[1][2], sacc[1][3]);
+        pa[0] = pack2<TM>(sacc[0][0], sacc[0][1]);
+        pa[1] = pack2<TM>(sacc[0][2], sacc[0][3]);
+        pa[2] = pack2<TM>(sacc[1][0], sacc[1][1]);
+        pa[3] = pack2<TM>(sacc[1][2], sacc[1][3]);
         // ---- O += P V ----
         if (!KV8) {
           const uint32_t vrow = vb + (uint32_t)(warp * 16 + (mat & 1) * 8 + l7) * 128u;
@@ -366,26 +372,33 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
             uint32_t bfr[4];
             const uint32_t chunk = (uint32_t)((np * 2 + (mat >> 1)) & 7);
             ldmatrix_x4_trans(bfr, vrow + (np >> 2) * (TN * 128) + ((chunk ^ (uint32_t)l7) << 4));
-            mma_16816<T>(o[2 * np], pa, bfr[0], bfr[1]);
-            mma_16816<T>(o[2 * np + 1], pa, bfr[2], bfr[3]);
+            mma_16816<TM>(o[2 * np], pa, bfr[0], bfr[1]);
+            mma_16816<TM>(o[2 * np + 1], pa, bfr[2], bfr[3]);
           }
         } else {
-          // fp8 V: the B fragment needs pairs of KEYS for one value column, i.e. bytes of different rows.
-          // Gather them with byte loads: keys {2tq, 2tq+1, 2tq+8, 2tq+9} of this warp's 16, column g + 8*nt.
-          const uint32_t r0 = (uint32_t)(warp * 16 + 2 * tq);
+          // fp8 V: the B fragment needs pairs of KEYS for one value column.  ldmatrix.trans on 16-bit units
+          // hands lane (g, tq) the byte pairs (dv 2g, 2g+1) of keys 2tq and 2tq+1; one byte permute splits them
+          // into an even-column and an odd-column fragment.  Accumulator tile 2c therefore holds value columns
+          // 16c + {0,2,..,14} and tile 2c+1 the odd ones: this lane ends up with 4 consecutive columns
+          // 16c + 4tq .. +3 of rows g and g+8 (undone when the result is written out).
+          const uint32_t vrow = vb + (uint32_t)(warp * 16 + (mat & 1) * 8 + l7) * 128u;
 #pragma unroll
-          for (int nt = 0; nt < HDV / 8; ++nt) {
-            const uint32_t col = (uint32_t)(nt * 8 + g);
-            uint32_t by[4];
+          for (int cp = 0; cp < HDV / 32; ++cp) {          // two 16-byte column chunks per ldmatrix.x4
+            uint32_t r4[4];
+            const uint32_t chunk = (uint32_t)(cp * 2 + (mat >> 1));
+            ldmatrix_x4_trans(r4, vrow + ((chunk ^ (uint32_t)l7) << 4));
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t r = r0 + (j & 1) + (j >> 1) * 8;
-              const uint32_t addr = vb + r * 128u + ((((col >> 4) ^ (r & 7u)) << 4) | (col & 15u));
-              asm volatile("ld.shared.u8 %0, [%1];" : "=r"(by[j]) : "r"(addr));
+            for (int h = 0; h < 2; ++h) {                  // r4[2h] = keys 0-7, r4[2h+1] = keys 8-15 of chunk 2cp+h
+              uint32_t xe, xo;
+              asm("prmt.b32 %0, %1, %2, 0x6420;" : "=r"(xe) : "r"(r4[2 * h]), "r"(r4[2 * h + 1]));
+              asm("prmt.b32 %0, %1, %2, 0x7531;" : "=r"(xo) : "r"(r4[2 * h]), "r"(r4[2 * h + 1]));
+              uint32_t e0, e1, o0, o1;
+              e4m3x4_to<TM>(xe, e0, e1);
+              e4m3x4_to<TM>(xo, o0, o1);
+              const int c = cp * 2 + h;
+              mma_16816<TM>(o[2 * c], pa, e0, e1);
+              mma_16816<TM>(o[2 * c + 1], pa, o0, o1);
             }
-            uint32_t b0, b1;
-            e4m3x4_to<T>(by[0] | (by[1] << 8) | (by[2] << 16) | (by[3] << 24), b0, b1);
-            mma_16816<T>(o[nt], pa, b0, b1);
           }
         }
       }
@@ -398,10 +411,20 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
         l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
         float* so = s_o + warp * 16 * SM::kLdO;
+        if (!KV8) {
 #pragma unroll
-        for (int nt = 0; nt < HDV / 8; ++nt) {
-          *reinterpret_cast<float2*>(so + g * SM::kLdO + nt * 8 + 2 * tq) = make_float2(o[nt][0], o[nt][1]);
-          *reinterpret_cast<float2*>(so + (g + 8) * SM::kLdO + nt * 8 + 2 * tq) = make_float2(o[nt][2], o[nt][3]);
+          for (int nt = 0; nt < HDV / 8; ++nt) {
+            *reinterpret_cast<float2*>(so + g * SM::kLdO + nt * 8 + 2 * tq) = make_float2(o[nt][0], o[nt][1]);
+            *reinterpret_cast<float2*>(so + (g + 8) * SM::kLdO + nt * 8 + 2 * tq) = make_float2(o[nt][2], o[nt][3]);
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < HDV / 16; ++c) {   // undo the even/odd column split of the fp8 V path
+            *reinterpret_cast<float4*>(so + g * SM::kLdO + c * 16 + 4 * tq) =
+                make_float4(o[2 * c][0], o[2 * c + 1][0], o[2 * c][1], o[2 * c + 1][1]);
+            *reinterpret_cast<float4*>(so + (g + 8) * SM::kLdO + c * 16 + 4 * tq) =
+                make_float4(o[2 * c][2], o[2 * c + 1][2], o[2 * c][3], o[2 * c + 1][3]);
+          }
         }
         if (tq == 0) {
           s_m[warp * 16 + g] = m_a; s_m[warp * 16 + g + 8] = m_b;

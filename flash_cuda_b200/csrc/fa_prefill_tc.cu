@@ -1,11 +1,12 @@
 // fa_prefill_tc.cu — the prefill mainloop on the 5th-generation tensor cores (tcgen05 + TMEM + TMA).
 //
 // One persistent CTA per SM.  A work item is a pair of adjacent 128-row query tiles of one (batch, q head);
-// both tiles share every K/V tile that TMA brings in.  Warp roles (320 threads):
+// both tiles share every K/V tile that TMA brings in.  Warp roles (384 threads):
 //   warps 0-3  softmax of tile 0   (one query row per thread: S row TMEM -> registers -> P row TMEM)
 //   warps 4-7  softmax of tile 1
 //   warp  8    MMA issuer: S_t = Q_t K^T (operands in shared memory), O_t += P_t V (P in TMEM)
 //   warp  9    TMA producer: Q pair, K ring, V ring (no cluster multicast: each CTA loads its own tiles)
+//   warps 10-11 idle (they complete the third warpgroup so that register tiers can be set per warpgroup)
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t overlays the first 64
 // columns of S_t once the owning thread has read its S row.
 // The tensor pipe runs [PV0(i), QK0(i+1), PV1(i), QK1(i+1)] so that one tile's softmax overlaps the other
@@ -29,7 +30,7 @@ namespace fa {
 namespace tc {
 
 constexpr int TM = 128, TN = 128;
-constexpr int NTHREADS = 320;
+constexpr int NTHREADS = 384;   // 12 warps: two softmax warpgroups + one warpgroup holding the MMA and TMA warps
 constexpr int WARP_MMA = 8, WARP_TMA = 9;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -160,6 +161,10 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   tc_fence_after_sync();
   const uint32_t tmem = *s_tmem;
 
+  // register tiers: the launch gives every thread 168; the MMA/TMA warpgroup hands most of its share to the
+  // two softmax warpgroups, which hold a full 128-wide fp32 score row per thread
+  if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
   if (warp == WARP_TMA) {
     // =========================================== TMA producer ===========================================
     if (lane == 0) {
@@ -344,7 +349,9 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     // drain: all MMAs this warp issued must have retired before TMEM is released
     if (leader) umma_commit(bar_drain);
     wait_or_abort(bar_drain, 0, s_abort + 1);
+  }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
     // ========================================= softmax + epilogue =======================================
     const int t = warp >> 2;                       // tile of this warpgroup
     const int r = (warp & 3) * 32 + lane;          // row within the tile == TMEM lane
@@ -417,11 +424,11 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           // eight independent chains instead of one 128-deep dependency chain
           float mxa[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) mxa[j] = __uint_as_float(sreg[0][j]);
+          for (int j = 0; j < 8; ++j) mxa[j] = -INFINITY;
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int j = (c == 0 ? 8 : 0); j < 32; ++j) mxa[j & 7] = fmaxf(mxa[j & 7], __uint_as_float(sreg[c][j]));
+            for (int j = 0; j < 32; ++j) mxa[j & 7] = fmaxf(mxa[j & 7], __uint_as_float(sreg[c][j]));
           mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
                      fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
         }
