@@ -58,7 +58,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -238,7 +238,7 @@ def run_ours(args) -> None:
     if not args.no_e2e:
         for i in range(2):
             e2e_step(i)
-        e2e_ms = _time_steps(e2e_step, max(3, args.steps // 2), dist, world)
+        e2e_ms = _time_steps(e2e_step, max(3, min(20, args.steps // 4)), dist, world)
         e2e = {"value": flops * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": _tensor_bytes(h_out)}
 
@@ -257,7 +257,7 @@ def run_ours(args) -> None:
 
             for i in range(max(args.warmup, 3)):
                 dstep(i)
-            dms = _time_steps(dstep, args.steps, dist, world)
+            dms = _time_steps(dstep, max(3, min(args.steps, 100)), dist, world)
             gbs = kvb / (dms * 1e-3) / 1e9
             decode = {
                 "metric": "paged decode HBM GB/s (B=128 q_len=1 ctx 1k..32k page 64 Hq=32 Hkv=8 d=128 bf16 KV, leftpad 0..63)",
@@ -288,6 +288,7 @@ def run_ours(args) -> None:
                      "frac": per_gpu / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
                      "kernel": "fwd_prefill_tc_kernel", "launch_ms": ms},
         "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks, "decode": decode, "cpu_baseline": cpu,
+        "kernels_per_step": {"prefill": ["fwd_prefill_tc_kernel"], "decode": ["sched_kernel", "fwd_decode_kernel"]},
     }
     print(json.dumps(line))
     if world > 1:
@@ -297,7 +298,7 @@ def run_ours(args) -> None:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the decode workload")
