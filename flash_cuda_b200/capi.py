@@ -15,6 +15,8 @@ import torch
 from . import build as _build
 
 FA_OK, FA_ERR_UNSUPPORTED, FA_ERR_BAD_ARG, FA_ERR_WORKSPACE, FA_ERR_NO_DEVICE, FA_ERR_LAUNCH, FA_ERR_DEVICE_TIMEOUT = range(7)
+FA_ERR_STATIC_LIMIT = 7
+STATIC_SCRATCH_BYTES = 8 << 20
 FA_DT_BF16, FA_DT_FP16, FA_DT_FP8_E4M3 = 0, 1, 2
 FA_ROUTE_AUTO, FA_ROUTE_PREFILL_TC, FA_ROUTE_DECODE, FA_ROUTE_GENERAL = 0, 1, 2, 3
 
@@ -22,6 +24,7 @@ EXPORTS = (
     "fa_b200_fwd_workspace_bytes", "fa_b200_fwd", "fa_b200_num_splits", "fa_b200_scheduler_metadata_len",
     "fa_b200_get_scheduler_metadata", "fa_b200_combine", "fa_b200_check_status", "fa_b200_strerror",
     "fa_b200_last_cuda_error", "fa_b200_version", "fa_b200_sizeof_fwd_params", "fa_b200_sizeof_sched_params",
+    "fa_b200_decode_fwd_static",
 )
 
 _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
@@ -87,6 +90,8 @@ def load(build_if_missing: bool = True):
     lib.fa_b200_strerror.argtypes = [C.c_int]
     lib.fa_b200_last_cuda_error.restype = C.c_char_p
     lib.fa_b200_version.restype = C.c_int
+    lib.fa_b200_decode_fwd_static.restype = C.c_int
+    lib.fa_b200_decode_fwd_static.argtypes = [C.POINTER(FaFwdParams), _vp]
     lib.fa_b200_sizeof_fwd_params.restype = C.c_size_t
     lib.fa_b200_sizeof_sched_params.restype = C.c_size_t
     if (lib.fa_b200_sizeof_fwd_params() != C.sizeof(FaFwdParams)
@@ -200,6 +205,22 @@ def fwd(q, k, v, *, out=None, workspace=None, check=False, **kw):
         check_status(workspace)
     del keep
     return out, lse, workspace
+
+
+def decode_fwd_static(q, k, v, *, out=None, **kw):
+    """Paged decode through `fa_b200_decode_fwd_static`: no workspace is passed and nothing is allocated by the
+    library (the output tensors here are the caller's).  Returns (out, lse)."""
+    lib = load()
+    total_q, hq, _ = q.shape
+    if out is None:
+        out = torch.empty(total_q, hq, v.shape[-1], device=q.device, dtype=q.dtype)
+    lse = torch.empty(hq, total_q, device=q.device, dtype=torch.float32)
+    p, keep = make_params(q, k, v, out, lse, **kw)
+    rc = lib.fa_b200_decode_fwd_static(C.byref(p), _stream())
+    if rc != FA_OK:
+        raise FaError(rc, "decode_fwd_static")
+    del keep
+    return out, lse
 
 
 def num_splits(q, k, v, **kw) -> int:

@@ -224,6 +224,7 @@ const char* fa_b200_strerror(int code) {
     case FA_ERR_NO_DEVICE: return "no sm_100 CUDA device";
     case FA_ERR_LAUNCH: return "CUDA call failed";
     case FA_ERR_DEVICE_TIMEOUT: return "a device-side wait timed out";
+    case FA_ERR_STATIC_LIMIT: return "problem needs more scratch than the 8 MiB built into fa_b200_decode_fwd_static";
     default: return "unknown error";
   }
 }
@@ -318,6 +319,39 @@ int fa_b200_fwd(const FaFwdParams* p, void* workspace, size_t workspace_bytes, f
                          "combine kernel");
   }
   return rc;
+}
+
+// ---- decode without allocation: scratch in a device array that is part of this library's image ----
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address: the address is looked up
+// once per device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+static __device__ __align__(256) unsigned char g_static_scratch[FA_B200_STATIC_SCRATCH_BYTES];
+static void* g_static_scratch_addr[64];
+static std::atomic<int> g_static_scratch_ready[64];
+
+int fa_b200_decode_fwd_static(const FaFwdParams* p, fa_stream_t stream) {
+  int rc = validate(p);
+  if (rc != FA_OK) return rc;
+  const DevInfo* di = device_info();
+  if (!di || !di->ok) return FA_ERR_NO_DEVICE;
+  Plan pl = make_plan(plan_input(p, di->sms));
+  if (pl.err != FA_OK) return pl.err;
+  if (pl.route != FA_ROUTE_DECODE) return FA_ERR_UNSUPPORTED;
+  if (ws_layout(p, pl).total > (size_t)FA_B200_STATIC_SCRATCH_BYTES) return FA_ERR_STATIC_LIMIT;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return FA_ERR_NO_DEVICE;
+  if (g_static_scratch_ready[dev].load(std::memory_order_acquire) == 0) {
+    std::lock_guard<std::mutex> lk(g_dev_mu);
+    if (g_static_scratch_ready[dev].load(std::memory_order_relaxed) == 0) {
+      void* addr = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&addr, g_static_scratch);   // this device's copy of the array
+      if (e != cudaSuccess || addr == nullptr) return cuda_fail(e, "cudaGetSymbolAddress(static scratch)");
+      g_static_scratch_addr[dev] = addr;
+      g_static_scratch_ready[dev].store(1, std::memory_order_release);
+    }
+  }
+  FaFwdParams q = *p;
+  q.route = FA_ROUTE_DECODE;
+  return fa_b200_fwd(&q, g_static_scratch_addr[dev], (size_t)FA_B200_STATIC_SCRATCH_BYTES, stream);
 }
 
 int fa_b200_scheduler_metadata_len(const FaSchedParams* p) {

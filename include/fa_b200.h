@@ -29,7 +29,8 @@ enum {
   FA_ERR_WORKSPACE = 3,     /* workspace too small */
   FA_ERR_NO_DEVICE = 4,     /* no sm_100 device / driver entry point missing */
   FA_ERR_LAUNCH = 5,        /* a CUDA call failed; see fa_b200_last_cuda_error() */
-  FA_ERR_DEVICE_TIMEOUT = 6 /* a bounded device-side wait ran out (read from the status word) */
+  FA_ERR_DEVICE_TIMEOUT = 6, /* a bounded device-side wait ran out (read from the status word) */
+  FA_ERR_STATIC_LIMIT = 7    /* problem needs more scratch than the built-in array of fa_b200_decode_fwd_static */
 };
 
 enum { FA_DT_BF16 = 0, FA_DT_FP16 = 1, FA_DT_FP8_E4M3 = 2 };
@@ -125,6 +126,25 @@ int fa_b200_combine(const float* o_part, const float* lse_part, int32_t nsplits,
  * wait that gave up. The reference has no counterpart: its device waits are unbounded
  * (kernels/fa4_blackwell.cu:5732). */
 int fa_b200_check_status(void* workspace, fa_stream_t stream, uint32_t* detail /* host, may be NULL */);
+
+/* Paged decode without any allocation, for callers that cannot obtain device memory at call time: an
+ * inference worker that handed every free byte of HBM to its KV-cache pool at start-up (a later cudaMalloc
+ * fails, or stalls the device while the driver looks for room), or a host written in another language that
+ * holds no device allocator at all.  It is fa_b200_fwd restricted to the decode route, with the scratch
+ * (status word, work counter, work list, split partials) living in an array compiled into this library
+ * instead of a caller-supplied workspace.  The caller still passes inputs and outputs in `p`.
+ *   - The array is FA_B200_STATIC_SCRATCH_BYTES (8 MiB) per GPU, held by every GPU that loads the library
+ *     until the process exits.  A problem whose scratch (fa_b200_fwd_workspace_bytes) exceeds it returns
+ *     FA_ERR_STATIC_LIMIT; a shape the decode route does not take returns FA_ERR_UNSUPPORTED.
+ *   - The first call on each device looks the array's device address up (with that device current); make that
+ *     first call before any stream capture begins.
+ *   - All calls on one GPU share the array and find the previous call's contents in it; the words that must
+ *     start at zero are cleared on `stream` at every call.  Two calls that overlap on the GPU (different
+ *     streams, no ordering between them) race on it: order them.
+ *   - fa_b200_check_status does not apply (there is no workspace pointer to hand it).
+ * Has no counterpart in the reference, which allocates its scratch with at::empty on every call. */
+#define FA_B200_STATIC_SCRATCH_BYTES (8u << 20)
+int fa_b200_decode_fwd_static(const FaFwdParams* p, fa_stream_t stream);
 
 const char* fa_b200_strerror(int code);      /* host string */
 const char* fa_b200_last_cuda_error(void);   /* host string of the last failed CUDA call on this thread */
