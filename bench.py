@@ -295,6 +295,62 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+def run_longctx(args) -> None:
+    """`--workload longctx`: B=1, a chunk of 4096 query rows against a paged KV of 524288 tokens (page 64),
+    128 heads, head_dim 192 / head_dim_v 128, causal, bf16.  The key range is split evenly over the ranks
+    (strong scaling); partial O / LSE are merged with ONE all-gather + the merge kernel, inside the timed region."""
+    from flash_cuda_b200 import multi_gpu as MG, ops, workloads as W
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist  # noqa: F811
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    ops.load(build_if_missing=False)
+    peaks = _peaks()
+    q_len, k_len, heads = 4096, args.longctx_keys, 128
+    per = k_len // world
+    p = W.long_context(dev, seed=0, q_len=q_len, k_len=k_len, heads=heads, k_begin=rank * per, k_end=(rank + 1) * per)
+    # unmasked pairs per head of the WHOLE problem: sum_i (k_len - q_len + i + 1)
+    pairs = q_len * (k_len - q_len) + q_len * (q_len + 1) // 2
+    flops = 2.0 * (192 + 128) * heads * pairs
+
+    def step(i):
+        MG.fwd_kv_sharded(p.q, p.k, p.v, page_table_local=p.page_table, seqused_k_local=p.seqused_k,
+                          cu_seqlens_q=p.cu_seqlens_q, max_seqlen_q=q_len, max_seqlen_k_local=per,
+                          softmax_scale=p.softmax_scale, causal=True, rank=rank, world=world)
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    steps = max(1, min(args.steps, 10))
+    ms = _time_steps(step, steps, dist, world)
+    clocks = sampler.stop() if rank == 0 else {}
+    if rank == 0:
+        val = flops / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "long-context prefill TFLOP/s (q 4096 x paged KV 524288, 128 heads, hd192/hdv128, causal, bf16), whole job",
+            "value": val, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (N(0,1) drawn on the device, seeded)",
+            "config": {"workload": f"long-context prefill q={q_len} k={k_len} heads={heads} hd192/hdv128 page 64",
+                       "parallelism": f"KV range split over {world} GPU(s); one all-gather of [O|LSE] + merge kernel",
+                       "l2": f"KV shard {p.k.numel() * 2 / 1e9 + p.v.numel() * 2 / 1e9:.1f} GB per GPU (> L2)"},
+            "roofline": {"bound": "tensor", "achieved": val / world, "peak": peaks["bf16_tflops_sustained"],
+                         "unit": "TFLOP/s", "frac": val / world / peaks["bf16_tflops_sustained"], "traffic": None,
+                         "peak_source": peaks["source"] + " (sustained: seconds-long step)"},
+            "gpu_launches": steps * (1 if world == 1 else 2), "clocks": clocks}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -306,9 +362,14 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--batch", type=int, default=4, help="prefill batch per GPU (4 = the benchmark configuration; "
                     "smaller values are for profiler captures only)")
+    ap.add_argument("--workload", default="prefill", choices=["prefill", "longctx"],
+                    help="prefill = the headline configuration (+ decode object); longctx = KV-range sharded long context")
+    ap.add_argument("--longctx-keys", type=int, default=524288)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "longctx":
+        run_longctx(args)
     else:
         run_ours(args)
 
