@@ -57,18 +57,19 @@ struct Smem {
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  // common case: a few probes (each probe already sleeps in hardware until the phase flips or a short time passes)
 #pragma unroll 1
-  for (int i = 0; i < 64; ++i)
+  for (int i = 0; i < 256; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  // slow case: keep probing; look at the abort flag and the SM clock only every 64 probes (about 2 s at 2 GHz)
+  const long long t0 = clock64();
 #pragma unroll 1
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    unsigned long long t1;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    if (t1 - t0 > 2000000000ull) return false;
+    if (clock64() - t0 > 4000000000ll) return false;
   }
 }
 

@@ -97,18 +97,19 @@ __device__ __forceinline__ Item decode_item(const TcArgs& a, int w) {
 
 // Bounded wait that also gives up when another role has raised the abort flag.
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  // common case: a few probes (each probe already sleeps in hardware until the phase flips or a short time passes)
 #pragma unroll 1
-  for (int i = 0; i < 64; ++i)
+  for (int i = 0; i < 256; ++i)
     if (mbar_try_wait(bar, parity)) return true;
-  unsigned long long t0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+  // slow case: keep probing; look at the abort flag and the SM clock only every 64 probes (about 2 s at 2 GHz)
+  const long long t0 = clock64();
 #pragma unroll 1
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    unsigned long long t1;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t1));
-    if (t1 - t0 > 2000000000ull) return false;   // 2 s
+    if (clock64() - t0 > 4000000000ll) return false;
   }
 }
 
@@ -146,8 +147,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     for (int s = 0; s < KST; ++s) { mbar_init(bar_k_full + 8 * s, 1); mbar_init(bar_k_empty + 8 * s, 1); }
     for (int s = 0; s < VST; ++s) { mbar_init(bar_v_full + 8 * s, 1); mbar_init(bar_v_empty + 8 * s, 1); }
     for (int t = 0; t < 2; ++t) {
-      mbar_init(bar_s_full + 8 * t, 1); mbar_init(bar_p_full + 8 * t, 128);
-      mbar_init(bar_o_full + 8 * t, 1); mbar_init(bar_o_empty + 8 * t, 128);
+      mbar_init(bar_s_full + 8 * t, 1); mbar_init(bar_p_full + 8 * t, 4);     // one elected arrival per softmax warp
+      mbar_init(bar_o_full + 8 * t, 1); mbar_init(bar_o_empty + 8 * t, 4);
     }
     mbar_init(bar_drain, 1);
     s_abort[0] = 0;
@@ -164,7 +165,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   // register tiers: the launch gives every thread 168; the MMA/TMA warpgroup hands most of its share to the
   // two softmax warpgroups, which hold a full 128-wide fp32 score row per thread
   if (warp >= 8) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
   if (warp == WARP_TMA) {
     // =========================================== TMA producer ===========================================
     if (lane == 0) {
@@ -254,30 +255,31 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
     constexpr uint32_t idesc_qk = umma_idesc(kFmt, TM, TN, false);
     constexpr uint32_t idesc_pv = umma_idesc(kFmt, TM, HDV, true);
+    // ONE thread runs this role.  The tensor pipe accepts only a few instructions ahead, so everything this
+    // thread does between two MMAs is time the pipe may idle: descriptors are built once and advanced by adds.
+    if (lane == 0) {
     uint32_t qcnt = 0, kcnt = 0, vcnt = 0, pcnt[2] = {0, 0}, oecnt[2] = {0, 0};
     bool ok = true;
-    const bool leader = lane == 0;
+    constexpr bool leader = true;
+    const uint64_t qd0 = umma_desc(sQ, 16, 1024), kd0 = umma_desc(sK, 16, 1024), vd0 = umma_desc(sV, TN * 128, 1024);
 
     auto issue_qk = [&](int t, uint32_t kslot) {
-      if (leader) {
-        const uint32_t qa = sQ + t * (TM * HD * 2), ka = sK + kslot * SM::kKStage;
+      const uint64_t qd = qd0 + (uint64_t)(t * ((TM * HD * 2) >> 4));
+      const uint64_t kd = kd0 + (uint64_t)(kslot * (SM::kKStage >> 4));
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * (TM * 128) + (ks & 3) * 32;
-          umma_ss<false>(tmem + t * TN, umma_desc(qa + off, 16, 1024), umma_desc(ka + off, 16, 1024), idesc_qk,
-                         ks > 0 ? 1u : 0u);
-        }
-        umma_commit(bar_s_full + 8 * t);
+      for (int ks = 0; ks < HD / 16; ++ks) {
+        constexpr int kBlk = (TM * 128) >> 4;
+        const uint64_t off = (uint64_t)((ks >> 2) * kBlk + (ks & 3) * 2);
+        umma_ss<false>(tmem + t * TN, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
       }
+      umma_commit(bar_s_full + 8 * t);
     };
     auto issue_pv = [&](int t, uint32_t vslot, bool first) {
-      if (leader) {
-        const uint32_t va = sV + vslot * SM::kVStage;
+      const uint64_t vd = vd0 + (uint64_t)(vslot * (SM::kVStage >> 4));
 #pragma unroll
-        for (int ks = 0; ks < TN / 16; ++ks)
-          umma_ts<false>(tmem + 256 + t * 128, tmem + t * TN + ks * 8, umma_desc(va + ks * 2048, TN * 128, 1024),
-                         idesc_pv, (!first || ks > 0) ? 1u : 0u);
-      }
+      for (int ks = 0; ks < TN / 16; ++ks)
+        umma_ts<false>(tmem + 256 + t * 128, tmem + t * TN + ks * 8, vd + (uint64_t)(ks * 128), idesc_pv,
+                       (!first || ks > 0) ? 1u : 0u);
     };
 
     for (int w = blockIdx.x; w < a.num_items && ok; w += gridDim.x) {
@@ -347,11 +349,12 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     }
     if (!ok) *s_abort = 1;
     // drain: all MMAs this warp issued must have retired before TMEM is released
-    if (leader) umma_commit(bar_drain);
+    umma_commit(bar_drain);
     wait_or_abort(bar_drain, 0, s_abort + 1);
+    }
   }
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     // ========================================= softmax + epilogue =======================================
     const int t = warp >> 2;                       // tile of this warpgroup
     const int r = (warp & 3) * 32 + lane;          // row within the tile == TMEM lane
@@ -477,7 +480,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         }
         tmem_wait_st();
         tc_fence_before_sync();
-        mbar_arrive(bar_p_full + 8 * t);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_p_full + 8 * t);
       }
       if (!ok) break;
 
@@ -524,7 +528,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       }
       if (had_blocks) {
         tc_fence_before_sync();
-        mbar_arrive(bar_o_empty + 8 * t);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_o_empty + 8 * t);
       }
       if (row_ok)
         p.lse[(int64_t)it.h * p.total_q + it.q0 + row] = l_fin > 0.f ? (m_fin + lg2(l_fin)) * kLn2 : -INFINITY;
