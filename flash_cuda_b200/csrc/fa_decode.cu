@@ -6,9 +6,9 @@
 //
 //   warp 4      producer: resolves page-table entries (32 at a time, one coalesced load) and streams whole
 //               pages with TMA 2-D boxes over the page pool viewed as [num_pages * page_size, hkv * hd] into a
-//               ring of 64-key stages (K 16 KB + V 16 KB each, 128-byte swizzle).  The ring runs on across
+//               ring of 32 KB stages (64 keys of 16-bit K+V, or 128 keys of e4m3 K+V; 128-byte swizzle).  The ring runs on across
 //               work-item boundaries; each stage carries a small descriptor (work id, first key, flags).
-//   warps 0-3   consumers: each takes 16 of the stage's 64 keys: S = Q K^T and O += P V with warp-level
+//   warps 0-3   consumers: each takes a quarter of the stage's keys: S = Q K^T and O += P V with warp-level
 //               MMA (ldmatrix from the swizzled stage), a private online softmax, and at the end of the work
 //               item a cross-warp merge through shared memory.
 // The tensor cores are incidental here: the roofline is HBM, the design goal is bytes in flight.
@@ -26,7 +26,7 @@
 namespace fa {
 namespace dec {
 
-constexpr int TN = 64;                 // keys per stage
+constexpr int TN = 64;                 // keys per scheduler block (metadata unit); a stage holds TNS keys
 constexpr int NCONS = 4;               // consumer warps
 constexpr int NTHREADS = (NCONS + 1) * 32;
 constexpr int HD = 128, HDV = 128;
@@ -44,7 +44,8 @@ struct DecArgs {
 
 template <int ESZ, int NST>
 struct Smem {
-  static constexpr int kKBytes = TN * HD * ESZ, kVBytes = TN * HDV * ESZ;
+  static constexpr int TNS = ESZ == 1 ? 128 : 64;   // keys per stage: 32 KB of K+V either way
+  static constexpr int kKBytes = TNS * HD * ESZ, kVBytes = TNS * HDV * ESZ;
   static constexpr int kStage = kKBytes + kVBytes;
   static constexpr int kRing = NST * kStage;
   static constexpr int kInfoOff = kRing;                       // NST x int4
@@ -52,7 +53,7 @@ struct Smem {
   static constexpr int kMiscOff = kBarOff + 2 * NST * 8;       // abort flags
   static constexpr int kScrOff = (kMiscOff + 16 + 15) / 16 * 16;
   static constexpr int kLdO = HDV + 4;
-  static constexpr int kScrBytes = NCONS * 16 * kLdO * 4 + 2 * NCONS * 16 * 4;
+  static constexpr int kScrBytes = NCONS * 16 * kLdO * 4 + 3 * NCONS * 16 * 4;
   static constexpr int kBytes = kScrOff + kScrBytes;
 };
 
@@ -108,8 +109,12 @@ __global__ void __launch_bounds__(NTHREADS, 1)
 fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   constexpr int ESZ = KV8 ? 1 : 2;
   using SM = Smem<ESZ, NST>;
-  // MMA element type: an fp8 cache is widened to fp16 (exact) and Q / P are taken to fp16 with it
-  using TM = typename std::conditional<KV8, __half, T>::type;
+  // 16-bit cache: m16n8k16 MMA in the cache's type.  e4m3 cache: m16n8k32 e4m3 MMA, fp32 accumulate; Q rows are
+  // quantised to e4m3 with a per-row scale (undone in the softmax scale) and P is rounded to e4m3.
+  using TM = T;
+  constexpr int TNS = SM::TNS;            // keys per stage
+  constexpr int WK = TNS / NCONS;         // keys per consumer warp and stage (16 or 32)
+  constexpr int NT = WK / 8;              // 8-key MMA column tiles per warp
   const KParams& p = a.kp;
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t raw = smem_u32(smem_dyn);
@@ -121,6 +126,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
   float* s_o = reinterpret_cast<float*>(sm + SM::kScrOff);
   float* s_m = s_o + NCONS * 16 * SM::kLdO;
   float* s_l = s_m + NCONS * 16;
+  float* s_lr = s_l + NCONS * 16;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
@@ -136,7 +142,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
     uint32_t cnt = 0;
     bool ok = true;
     const int ps = p.page_size;
-    const int boxes = TN / a.box_rows;          // TMA boxes per stage and 128-byte column block
+    const int boxes = TNS / a.box_rows;         // TMA boxes per stage and 128-byte column block
     while (ok) {
       int w = 0;
       if (lane == 0) w = atomicAdd(p.counters, 1);
@@ -157,8 +163,8 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
       }
       const int npages = (it.seqlen_k + ps - 1) / ps;
       int cache_first = -1, cache_id = 0;       // 32 page-table entries, one per lane
-      for (int nb = it.lo; nb < it.hi && ok; ++nb) {
-        const int key0 = nb * TN;
+      const int key_end = it.hi * TN;
+      for (int key0 = it.lo * TN; key0 < key_end && ok; key0 += TNS) {
         const int lp0 = key0 / ps;              // first logical page of this stage
         if (cache_first < 0 || lp0 < cache_first || lp0 + boxes > cache_first + 32) {
           cache_first = lp0;
@@ -171,8 +177,8 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         const uint32_t kdst = base + s * SM::kStage, vdst = kdst + SM::kKBytes;
         if (lane == 0) {
           int flags = 0;
-          if (nb == it.lo) flags |= F_FIRST;
-          if (nb + 1 == it.hi) flags |= F_LAST;
+          if (key0 == it.lo * TN) flags |= F_FIRST;
+          if (key0 + TNS >= key_end) flags |= F_LAST;
           s_info[4 * s] = w; s_info[4 * s + 1] = key0; s_info[4 * s + 2] = flags;
           mbar_expect_tx(bar_full + 8 * s, SM::kStage);
         }
@@ -181,7 +187,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
           const int lp = kk / ps;
           const int pid = __shfl_sync(0xffffffffu, cache_id, lp - cache_first);
           if (lane == 0) {
-            const int y = (kk < it.seqlen_k && pid >= 0) ? pid * ps + (kk - lp * ps) : a.kv_total_rows;
+            const int y = (kk < it.seqlen_k && kk < key_end && pid >= 0) ? pid * ps + (kk - lp * ps) : a.kv_total_rows;
             const uint32_t roff = (uint32_t)(j * a.box_rows) * 128u;
             if (KV8) {
               tma_load_2d(kdst + roff, &map_k, it.hk * HD, y, bar_full + 8 * s);
@@ -189,8 +195,8 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
             } else {
 #pragma unroll
               for (int cb = 0; cb < 2; ++cb) {
-                tma_load_2d(kdst + cb * (TN * 128) + roff, &map_k, it.hk * HD + cb * 64, y, bar_full + 8 * s);
-                tma_load_2d(vdst + cb * (TN * 128) + roff, &map_v, it.hk * HDV + cb * 64, y, bar_full + 8 * s);
+                tma_load_2d(kdst + cb * (TNS * 128) + roff, &map_k, it.hk * HD + cb * 64, y, bar_full + 8 * s);
+                tma_load_2d(vdst + cb * (TNS * 128) + roff, &map_v, it.hk * HDV + cb * 64, y, bar_full + 8 * s);
               }
             }
           }
@@ -217,9 +223,11 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
     const int rep = p.rep;
     uint32_t cnt = 0;
     bool ok = true;
-    uint32_t qf[HD / 16][4];
+    uint32_t qf[HD / 16][4];   // 16-bit: 8 k-steps of 16; e4m3: the first 4 entries are 4 k-steps of 32
+    float qs_a = 1.f, qs_b = 1.f;   // e4m3 Q: 1 / (row quantisation scale), folded into the logit scale
     float o[HDV / 8][4];
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    float lr_a = 0.f, lr_b = 0.f;   // e4m3 cache: sums of the ROUNDED probabilities (normalise O); l_* stay exact for the LSE
     int lo_a = 0, hi_a = -1, lo_b = 0, hi_b = -1, lo_max = 0, hi_min = -1;
     float c_mul = 0.f, cap_in = 0.f, vds = 1.f;
     WorkItem it{};
@@ -235,28 +243,71 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
       if (flags & F_FIRST) {
         it = decode_work(p, info.x);
         const int rows_total = it.seqlen_q * rep;
-        // Q fragments straight from global memory (A operand of m16n8k16; rows g and g+8)
+        // Q fragments straight from global memory (rows g and g+8 of the packed tile)
+        if constexpr (!KV8) {
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
+          for (int ks = 0; ks < HD / 16; ++ks) {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int R = g + (e & 1) * 8;
-            // 16-bit KV: columns ks*16 + 2*tq (+8); fp8 KV: the contraction index is permuted to match the
-            // byte order ldmatrix delivers (see k_fragment): columns (ks>>1)*32 + (ks&1)*16 + 4*tq + 2*(e>>1)
-            const int c = KV8 ? ((ks >> 1) * 32 + (ks & 1) * 16 + 4 * tq + 2 * (e >> 1)) : (ks * 16 + 2 * tq + (e >> 1) * 8);
-            uint32_t v = 0;
-            if (R < rows_total) {
-              const int token = R / rep, head = it.hk * rep + R % rep;
-              v = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(p.q) +
-                                                     (int64_t)(it.q0 + token) * p.q_row_stride +
-                                                     (int64_t)head * p.q_head_stride + c);
-              if (KV8 && std::is_same<T, __nv_bfloat16>::value) {   // bf16 -> fp16, clamped to the fp16 range
-                const float lo16 = __uint_as_float(v << 16), hi16 = __uint_as_float(v & 0xffff0000u);
-                v = pack2<__half>(fminf(fmaxf(lo16, -65504.f), 65504.f), fminf(fmaxf(hi16, -65504.f), 65504.f));
+            for (int e = 0; e < 4; ++e) {      // A operand of m16n8k16: columns ks*16 + 2*tq (+8)
+              const int R = g + (e & 1) * 8;
+              const int c = ks * 16 + 2 * tq + (e >> 1) * 8;
+              uint32_t v = 0;
+              if (R < rows_total) {
+                const int token = R / rep, head = it.hk * rep + R % rep;
+                v = *reinterpret_cast<const uint32_t*>(reinterpret_cast<const T*>(p.q) +
+                                                       (int64_t)(it.q0 + token) * p.q_row_stride +
+                                                       (int64_t)head * p.q_head_stride + c);
               }
+              qf[ks][e] = v;
             }
-            qf[ks][e] = v;
           }
+        } else {
+          // A operand of m16n8k32 (e4m3): a0/a1 = rows g/g+8, columns 32k + 4tq..+3; a2/a3 = columns 32k + 16 + 4tq..+3.
+          // Each row is scaled so that its largest magnitude lands at 224 before rounding to e4m3.
+          float qv[2][HD / 32][2][4];
+          float amax[2] = {0.f, 0.f};
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            const int R = g + rr * 8;
+            const bool live = R < rows_total;
+            const int token = R / rep, head = it.hk * rep + R % rep;
+            const T* qrow = reinterpret_cast<const T*>(p.q) + (int64_t)(it.q0 + (live ? token : 0)) * p.q_row_stride +
+                            (int64_t)(live ? head : 0) * p.q_head_stride;
+#pragma unroll
+            for (int k32 = 0; k32 < HD / 32; ++k32)
+#pragma unroll
+              for (int part = 0; part < 2; ++part) {
+                uint2 raw = make_uint2(0u, 0u);
+                if (live) raw = *reinterpret_cast<const uint2*>(qrow + k32 * 32 + part * 16 + 4 * tq);
+                float f[4];
+                if (std::is_same<T, __nv_bfloat16>::value) {
+                  f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);
+                  f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xffff0000u);
+                } else {
+                  const float2 lo2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                  const float2 hi2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                  f[0] = lo2.x; f[1] = lo2.y; f[2] = hi2.x; f[3] = hi2.y;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { qv[rr][k32][part][j] = f[j]; amax[rr] = fmaxf(amax[rr], fabsf(f[j])); }
+              }
+          }
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            amax[rr] = fmaxf(amax[rr], __shfl_xor_sync(0xffffffffu, amax[rr], 1));
+            amax[rr] = fmaxf(amax[rr], __shfl_xor_sync(0xffffffffu, amax[rr], 2));
+          }
+          const float sq_a = amax[0] > 0.f ? 224.f / amax[0] : 1.f, sq_b = amax[1] > 0.f ? 224.f / amax[1] : 1.f;
+          qs_a = 1.f / sq_a; qs_b = 1.f / sq_b;
+#pragma unroll
+          for (int k32 = 0; k32 < HD / 32; ++k32)
+#pragma unroll
+            for (int part = 0; part < 2; ++part) {
+              qf[k32][2 * part] = pack4_e4m3(qv[0][k32][part][0] * sq_a, qv[0][k32][part][1] * sq_a,
+                                             qv[0][k32][part][2] * sq_a, qv[0][k32][part][3] * sq_a);
+              qf[k32][2 * part + 1] = pack4_e4m3(qv[1][k32][part][0] * sq_b, qv[1][k32][part][1] * sq_b,
+                                                 qv[1][k32][part][2] * sq_b, qv[1][k32][part][3] * sq_b);
+            }
         }
         float sc = p.scale;
         vds = 1.f;
@@ -268,17 +319,17 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         const int off = it.seqlen_k - it.seqlen_q;
         const int qp_a = off + g / rep, qp_b = off + (g + 8) / rep;
         lo_a = lo_b = it.leftpad;
-        hi_a = hi_b = it.seqlen_k - 1;
+        hi_a = hi_b = min(it.seqlen_k, it.hi * TN) - 1;   // keys past this split's range are not ours
         if (p.is_causal) { hi_a = min(hi_a, qp_a); hi_b = min(hi_b, qp_b); }
         if (p.window_right >= 0) { hi_a = min(hi_a, qp_a + p.window_right); hi_b = min(hi_b, qp_b + p.window_right); }
         if (p.window_left >= 0) { lo_a = max(lo_a, qp_a - p.window_left); lo_b = max(lo_b, qp_b - p.window_left); }
         // bounds valid for all 16 rows (rows past rows_total included: conservative)
         const int qp_lo = off, qp_hi = off + 15 / rep;
-        lo_max = it.leftpad; hi_min = it.seqlen_k - 1;
+        lo_max = it.leftpad; hi_min = min(it.seqlen_k, it.hi * TN) - 1;
         if (p.is_causal) hi_min = min(hi_min, qp_lo);
         if (p.window_right >= 0) hi_min = min(hi_min, qp_lo + p.window_right);
         if (p.window_left >= 0) lo_max = max(lo_max, qp_hi - p.window_left);
-        m_a = m_b = -INFINITY; l_a = l_b = 0.f;
+        m_a = m_b = -INFINITY; l_a = l_b = 0.f; lr_a = lr_b = 0.f;
 #pragma unroll
         for (int i = 0; i < HDV / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
       }
@@ -286,50 +337,48 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
       if (!(flags & F_EMPTY)) {
         const uint32_t kb = base + s * SM::kStage, vb = kb + SM::kKBytes;
         const int mat = lane >> 3, l7 = lane & 7;
-        float sacc[2][4];
+        float sacc[NT][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) { sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f; }
-        if (!KV8) {
-          const uint32_t krow = kb + (uint32_t)(warp * 16 + (mat >> 1) * 8 + l7) * 128u;
+        for (int i = 0; i < NT; ++i) { sacc[i][0] = sacc[i][1] = sacc[i][2] = sacc[i][3] = 0.f; }
+        if constexpr (!KV8) {
+          const uint32_t krow = kb + (uint32_t)(warp * WK + (mat >> 1) * 8 + l7) * 128u;
 #pragma unroll
           for (int ks = 0; ks < HD / 16; ++ks) {
             uint32_t bfr[4];
             const uint32_t chunk = (uint32_t)((ks * 2 + (mat & 1)) & 7);
-            ldmatrix_x4(bfr, krow + (ks >> 2) * (TN * 128) + ((chunk ^ (uint32_t)l7) << 4));
+            ldmatrix_x4(bfr, krow + (ks >> 2) * (TNS * 128) + ((chunk ^ (uint32_t)l7) << 4));
             mma_16816<TM>(sacc[0], qf[ks], bfr[0], bfr[1]);
             mma_16816<TM>(sacc[1], qf[ks], bfr[2], bfr[3]);
           }
         } else {
-          // fp8 rows are 128 bytes: one swizzle row per key.  ldmatrix moves 16-byte chunks, so a lane ends up
-          // with 4 consecutive e4m3 values of key (lane/4); they are widened in registers and fed to the
-          // 16-bit MMA with the contraction index permuted consistently on the Q side.
-          const uint32_t krow = kb + (uint32_t)(warp * 16 + (mat >> 1) * 8 + l7) * 128u;
+          // e4m3 rows are 128 bytes: one swizzle row per key.  ldmatrix moves 16-byte chunks, so lane (g, tq)
+          // receives bytes 4tq..4tq+3 of key g: exactly the B operand of m16n8k32, no conversion needed.
 #pragma unroll
-          for (int k32 = 0; k32 < HD / 32; ++k32) {
-            uint32_t raw4[4];
-            const uint32_t chunk = (uint32_t)(k32 * 2 + (mat & 1));
-            ldmatrix_x4(raw4, krow + ((chunk ^ (uint32_t)l7) << 4));
-            uint32_t b00, b01, b10, b11, b20, b21, b30, b31;
-            e4m3x4_to<TM>(raw4[0], b00, b01);   // keys 0-7, bytes 32*k32 + 4tq .. +3
-            e4m3x4_to<TM>(raw4[1], b10, b11);   // keys 0-7, bytes 32*k32 + 16 + 4tq .. +3
-            e4m3x4_to<TM>(raw4[2], b20, b21);   // keys 8-15
-            e4m3x4_to<TM>(raw4[3], b30, b31);
-            mma_16816<TM>(sacc[0], qf[2 * k32], b00, b01);
-            mma_16816<TM>(sacc[0], qf[2 * k32 + 1], b10, b11);
-            mma_16816<TM>(sacc[1], qf[2 * k32], b20, b21);
-            mma_16816<TM>(sacc[1], qf[2 * k32 + 1], b30, b31);
+          for (int hf = 0; hf < 2; ++hf) {
+            const uint32_t krow = kb + (uint32_t)(warp * WK + hf * 16 + (mat >> 1) * 8 + l7) * 128u;
+#pragma unroll
+            for (int k32 = 0; k32 < HD / 32; ++k32) {
+              uint32_t raw4[4];
+              const uint32_t chunk = (uint32_t)(k32 * 2 + (mat & 1));
+              ldmatrix_x4(raw4, krow + ((chunk ^ (uint32_t)l7) << 4));
+              mma_16832_e4m3(sacc[2 * hf], qf[k32], raw4[0], raw4[1]);
+              mma_16832_e4m3(sacc[2 * hf + 1], qf[k32], raw4[2], raw4[3]);
+            }
           }
         }
-        // ---- mask + online softmax over this warp's 16 keys ----
-        const int kbase = key0 + warp * 16;
-        const bool full = (kbase >= lo_max) && (kbase + 15 <= hi_min);
+        // ---- mask + online softmax over this warp's keys ----
+        const int kbase = key0 + warp * WK;
+        const bool full = (kbase >= lo_max) && (kbase + WK - 1 <= hi_min);
+        const float cm_a = c_mul * (has_cap ? 1.f : qs_a), cm_b = c_mul * (has_cap ? 1.f : qs_b);
+        const float ci_a = cap_in * qs_a, ci_b = cap_in * qs_b;
         float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float y = sacc[nt][e];
-            y = has_cap ? tanh_fast(y * cap_in) * c_mul : y * c_mul;
+            if (e >= 2) y = has_cap ? tanh_fast(y * ci_b) * c_mul : y * cm_b;
+            else y = has_cap ? tanh_fast(y * ci_a) * c_mul : y * cm_a;
             if (!full) {
               const int kk = kbase + nt * 8 + 2 * tq + (e & 1);
               const bool okk = e >= 2 ? (kk >= lo_b && kk <= hi_b) : (kk >= lo_a && kk <= hi_a);
@@ -348,11 +397,27 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         m_a = mn_a; m_b = mn_b;
         float ps_a = 0.f, ps_b = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
+        for (int nt = 0; nt < NT; ++nt) {
           sacc[nt][0] = ex2(sacc[nt][0] - ms_a); sacc[nt][1] = ex2(sacc[nt][1] - ms_a);
           sacc[nt][2] = ex2(sacc[nt][2] - ms_b); sacc[nt][3] = ex2(sacc[nt][3] - ms_b);
           ps_a += sacc[nt][0] + sacc[nt][1];
           ps_b += sacc[nt][2] + sacc[nt][3];
+        }
+        uint32_t pa8[4];
+        if constexpr (KV8) {
+          // P as e4m3; the row sums are taken over the ROUNDED probabilities so that numerator and denominator
+          // describe the same weights
+          pa8[0] = pack4_e4m3(sacc[0][0], sacc[0][1], sacc[1][0], sacc[1][1]);
+          pa8[1] = pack4_e4m3(sacc[0][2], sacc[0][3], sacc[1][2], sacc[1][3]);
+          pa8[2] = pack4_e4m3(sacc[2][0], sacc[2][1], sacc[3][0], sacc[3][1]);
+          pa8[3] = pack4_e4m3(sacc[2][2], sacc[2][3], sacc[3][2], sacc[3][3]);
+          auto sum4 = [](uint32_t q4) {
+            const uint32_t h0 = e4m3x2_to_f16x2((uint16_t)(q4 & 0xffffu)), h1 = e4m3x2_to_f16x2((uint16_t)(q4 >> 16));
+            const float2 f = __half22float2(__hadd2(*reinterpret_cast<const __half2*>(&h0), *reinterpret_cast<const __half2*>(&h1)));
+            return f.x + f.y;
+          };
+          lr_a = lr_a * corr_a + sum4(pa8[0]) + sum4(pa8[2]);
+          lr_b = lr_b * corr_b + sum4(pa8[1]) + sum4(pa8[3]);
         }
         l_a = l_a * corr_a + ps_a;
         l_b = l_b * corr_b + ps_b;
@@ -360,46 +425,43 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
 #pragma unroll
           for (int i = 0; i < HDV / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
         }
-        uint32_t pa[4];
-        pa[0] = pack2<TM>(sacc[0][0], sacc[0][1]);
-        pa[1] = pack2<TM>(sacc[0][2], sacc[0][3]);
-        pa[2] = pack2<TM>(sacc[1][0], sacc[1][1]);
-        pa[3] = pack2<TM>(sacc[1][2], sacc[1][3]);
         // ---- O += P V ----
-        if (!KV8) {
-          const uint32_t vrow = vb + (uint32_t)(warp * 16 + (mat & 1) * 8 + l7) * 128u;
+        if constexpr (!KV8) {
+          uint32_t pa[4];
+          pa[0] = pack2<TM>(sacc[0][0], sacc[0][1]);
+          pa[1] = pack2<TM>(sacc[0][2], sacc[0][3]);
+          pa[2] = pack2<TM>(sacc[1][0], sacc[1][1]);
+          pa[3] = pack2<TM>(sacc[1][2], sacc[1][3]);
+          const uint32_t vrow = vb + (uint32_t)(warp * WK + (mat & 1) * 8 + l7) * 128u;
 #pragma unroll
           for (int np = 0; np < HDV / 16; ++np) {
             uint32_t bfr[4];
             const uint32_t chunk = (uint32_t)((np * 2 + (mat >> 1)) & 7);
-            ldmatrix_x4_trans(bfr, vrow + (np >> 2) * (TN * 128) + ((chunk ^ (uint32_t)l7) << 4));
+            ldmatrix_x4_trans(bfr, vrow + (np >> 2) * (TNS * 128) + ((chunk ^ (uint32_t)l7) << 4));
             mma_16816<TM>(o[2 * np], pa, bfr[0], bfr[1]);
             mma_16816<TM>(o[2 * np + 1], pa, bfr[2], bfr[3]);
           }
         } else {
-          // fp8 V: the B fragment needs pairs of KEYS for one value column.  ldmatrix.trans on 16-bit units
-          // hands lane (g, tq) the byte pairs (dv 2g, 2g+1) of keys 2tq and 2tq+1; one byte permute splits them
-          // into an even-column and an odd-column fragment.  Accumulator tile 2c therefore holds value columns
-          // 16c + {0,2,..,14} and tile 2c+1 the odd ones: this lane ends up with 4 consecutive columns
-          // 16c + 4tq .. +3 of rows g and g+8 (undone when the result is written out).
-          const uint32_t vrow = vb + (uint32_t)(warp * 16 + (mat & 1) * 8 + l7) * 128u;
+          // P as the e4m3 A operand of m16n8k32.  This lane holds keys {2tq, 2tq+1} of each 8-key tile; contraction
+          // slots 4tq..4tq+3 take the pairs of tiles 0 and 1, slots 16+4tq.. those of tiles 2 and 3.
+          const uint32_t (&pa)[4] = pa8;
+          // V: the B operand needs 4 KEYS of one value column per register, i.e. bytes of different rows.
+          // ldmatrix.trans on 16-bit units hands lane (g, tq) the byte pairs (columns 2g, 2g+1) of keys 2tq and
+          // 2tq+1 of each 8-key group; one byte permute per register pair gathers the four keys of the even
+          // column and of the odd column, in the same slot order as P above.  Accumulator tile 2c therefore holds
+          // value columns 16c + {0,2,..,14} and tile 2c+1 the odd ones (undone when the result is written out).
+          const uint32_t vrow = vb + (uint32_t)(warp * WK + mat * 8 + l7) * 128u;
 #pragma unroll
-          for (int cp = 0; cp < HDV / 32; ++cp) {          // two 16-byte column chunks per ldmatrix.x4
+          for (int c = 0; c < HDV / 16; ++c) {
             uint32_t r4[4];
-            const uint32_t chunk = (uint32_t)(cp * 2 + (mat >> 1));
-            ldmatrix_x4_trans(r4, vrow + ((chunk ^ (uint32_t)l7) << 4));
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {                  // r4[2h] = keys 0-7, r4[2h+1] = keys 8-15 of chunk 2cp+h
-              uint32_t xe, xo;
-              asm("prmt.b32 %0, %1, %2, 0x6420;" : "=r"(xe) : "r"(r4[2 * h]), "r"(r4[2 * h + 1]));
-              asm("prmt.b32 %0, %1, %2, 0x7531;" : "=r"(xo) : "r"(r4[2 * h]), "r"(r4[2 * h + 1]));
-              uint32_t e0, e1, o0, o1;
-              e4m3x4_to<TM>(xe, e0, e1);
-              e4m3x4_to<TM>(xo, o0, o1);
-              const int c = cp * 2 + h;
-              mma_16816<TM>(o[2 * c], pa, e0, e1);
-              mma_16816<TM>(o[2 * c + 1], pa, o0, o1);
-            }
+            ldmatrix_x4_trans(r4, vrow + (((uint32_t)c ^ (uint32_t)l7) << 4));
+            uint32_t e0, e1, o0, o1;
+            asm("prmt.b32 %0, %1, %2, 0x6420;" : "=r"(e0) : "r"(r4[0]), "r"(r4[1]));
+            asm("prmt.b32 %0, %1, %2, 0x6420;" : "=r"(e1) : "r"(r4[2]), "r"(r4[3]));
+            asm("prmt.b32 %0, %1, %2, 0x7531;" : "=r"(o0) : "r"(r4[0]), "r"(r4[1]));
+            asm("prmt.b32 %0, %1, %2, 0x7531;" : "=r"(o1) : "r"(r4[2]), "r"(r4[3]));
+            mma_16832_e4m3(o[2 * c], pa, e0, e1);
+            mma_16832_e4m3(o[2 * c + 1], pa, o0, o1);
           }
         }
       }
@@ -411,6 +473,8 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         // ---- merge the four warps' partial results and write the output rows ----
         l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
         l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        lr_a += __shfl_xor_sync(0xffffffffu, lr_a, 1); lr_a += __shfl_xor_sync(0xffffffffu, lr_a, 2);
+        lr_b += __shfl_xor_sync(0xffffffffu, lr_b, 1); lr_b += __shfl_xor_sync(0xffffffffu, lr_b, 2);
         float* so = s_o + warp * 16 * SM::kLdO;
         if (!KV8) {
 #pragma unroll
@@ -430,6 +494,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         if (tq == 0) {
           s_m[warp * 16 + g] = m_a; s_m[warp * 16 + g + 8] = m_b;
           s_l[warp * 16 + g] = l_a; s_l[warp * 16 + g + 8] = l_b;
+          s_lr[warp * 16 + g] = lr_a; s_lr[warp * 16 + g + 8] = lr_b;
         }
         bar_consumers();
         {
@@ -438,13 +503,14 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
           float mw[NCONS], M = -INFINITY;
 #pragma unroll
           for (int wi = 0; wi < NCONS; ++wi) { mw[wi] = s_m[wi * 16 + R]; M = fmaxf(M, mw[wi]); }
-          float L = 0.f, acc[16];
+          float L = 0.f, Lr = 0.f, acc[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) acc[j] = 0.f;
 #pragma unroll
           for (int wi = 0; wi < NCONS; ++wi) {
             const float e = mw[wi] == -INFINITY ? 0.f : ex2(mw[wi] - M);
             L += e * s_l[wi * 16 + R];
+            Lr += e * s_lr[wi * 16 + R];
             const float* src = s_o + (wi * 16 + R) * SM::kLdO + c0;
 #pragma unroll
             for (int j = 0; j < 16; j += 4) {
@@ -456,7 +522,8 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
             const int token = R / rep, head = it.hk * rep + R % rep;
             const int64_t qi = it.q0 + token;
             if (p.nsplits > 1) {
-              const float inv = L > 0.f ? vds / L : 0.f;
+              const float Ln = KV8 ? Lr : L;   // e4m3: divide by the sum of the rounded probabilities
+              const float inv = Ln > 0.f ? vds / Ln : 0.f;
               float* op = p.o_part + (((int64_t)it.split * p.total_q + qi) * p.hq + head) * p.hdv + c0;
 #pragma unroll
               for (int j = 0; j < 16; j += 4)
@@ -470,9 +537,11 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
                 const float mn = fmaxf(M, ys);
                 osc = M == -INFINITY ? 0.f : ex2(M - mn);
                 L = L * osc + ex2(ys - mn);
+                Lr = Lr * osc + ex2(ys - mn);
                 M = mn;
               }
-              const float inv = L > 0.f ? osc * vds / L : 0.f;
+              const float Ln = KV8 ? Lr : L;
+              const float inv = Ln > 0.f ? osc * vds / Ln : 0.f;
               T* op = reinterpret_cast<T*>(p.out) + qi * p.o_row_stride + (int64_t)head * p.o_head_stride + c0;
               uint4 v0, v1;
               v0.x = pack2<T>(acc[0] * inv, acc[1] * inv);   v0.y = pack2<T>(acc[2] * inv, acc[3] * inv);
@@ -533,7 +602,8 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
   DecArgs a;
   a.kp = kp;
   a.total_work = num_work_slots * kp.hkv * kp.nsplits;
-  a.box_rows = kp.page_size < TN ? kp.page_size : TN;
+  constexpr int TNS = SM::TNS;
+  a.box_rows = kp.page_size < TNS ? kp.page_size : TNS;
   const uint64_t rows = (uint64_t)kp.num_pages * (uint64_t)kp.page_size;
   a.kv_total_rows = (int)rows;
   const int kvdt = KV8 ? FA_DT_FP8_E4M3 : (std::is_same<T, __half>::value ? FA_DT_FP16 : FA_DT_BF16);
@@ -567,8 +637,8 @@ int launch_decode(const KParams& kp, const Plan& pl, int compute_dtype, cudaStre
   const int slots = kp.batch * pl.max_mtiles;
   const bool bf = compute_dtype != FA_DT_FP16;
   if (kp.kv_fp8)
-    return bf ? dec::launch_t<__nv_bfloat16, true, 10>(kp, pl, slots, stream)
-              : dec::launch_t<__half, true, 10>(kp, pl, slots, stream);
+    return bf ? dec::launch_t<__nv_bfloat16, true, 5>(kp, pl, slots, stream)
+              : dec::launch_t<__half, true, 5>(kp, pl, slots, stream);
   return bf ? dec::launch_t<__nv_bfloat16, false, 5>(kp, pl, slots, stream)
             : dec::launch_t<__half, false, 5>(kp, pl, slots, stream);
 }

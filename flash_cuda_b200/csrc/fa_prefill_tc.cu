@@ -45,11 +45,24 @@ struct TcArgs {
   int kv_total_rows; // rows of the K/V tensor map (out-of-range y => zero fill)
 };
 
-template <int HD, int HDV, int KST, int VST>
+struct fp8_t { unsigned char x; };   // tag type: Q, K, V and P are e4m3 bytes, the output is bf16
+
+template <typename T> struct Elem {
+  static constexpr int kSize = 2;
+  static constexpr bool kF8 = false;
+  using Out = T;
+};
+template <> struct Elem<fp8_t> {
+  static constexpr int kSize = 1;
+  static constexpr bool kF8 = true;
+  using Out = __nv_bfloat16;
+};
+
+template <int ESZ, int HD, int HDV, int KST, int VST>
 struct Smem {
-  static constexpr int kQBytes = 2 * TM * HD * 2;
-  static constexpr int kKStage = TN * HD * 2;
-  static constexpr int kVStage = TN * HDV * 2;
+  static constexpr int kQBytes = 2 * TM * HD * ESZ;
+  static constexpr int kKStage = TN * HD * ESZ;
+  static constexpr int kVStage = TN * HDV * ESZ;
   static constexpr int kBarOff = kQBytes + KST * kKStage + VST * kVStage;
   static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1;
   static constexpr int kBytes = kBarOff + kNumBars * 8 + 16;
@@ -95,6 +108,16 @@ __device__ __forceinline__ Item decode_item(const TcArgs& a, int w) {
   return it;
 }
 
+// Position in a ring of N stages: slot index and phase bit, advanced without divisions.
+template <int N>
+struct Ring {
+  uint32_t slot = 0, phase = 0, n = 0;
+  __device__ __forceinline__ void advance() {
+    ++n;
+    if (++slot == (uint32_t)N) { slot = 0; phase ^= 1u; }
+  }
+};
+
 // Bounded wait that also gives up when another role has raised the abort flag.
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   // common case: a few probes (each probe already sleeps in hardware until the phase flips or a short time passes)
@@ -117,10 +140,15 @@ template <typename T, int HD, int HDV, int KST, int VST>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
-  using SM = Smem<HD, HDV, KST, VST>;
+  constexpr int ESZ = Elem<T>::kSize;          // bytes per Q/K/V element
+  constexpr bool F8 = Elem<T>::kF8;
+  constexpr int EPB = 128 / ESZ;               // elements per 128-byte swizzle row
+  using TO = typename Elem<T>::Out;
+  using SM = Smem<ESZ, HD, HDV, KST, VST>;
   const KParams& p = a.kp;
   extern __shared__ unsigned char smem_dyn[];
-  // 1024-byte alignment for the 128-byte swizzle atoms
+  // 1024-byte alignment for the 128-byte swizzle atoms, by rounding up inside a request that carries 1 KB of slack.
+  // (Declaring the array __align__(1024) instead measured 10 % slower on B200 with identical tile addresses.)
   const uint32_t raw = smem_u32(smem_dyn);
   const uint32_t base = (raw + 1023u) & ~1023u;
   unsigned char* sm = smem_dyn + (base - raw);
@@ -169,7 +197,9 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   if (warp == WARP_TMA) {
     // =========================================== TMA producer ===========================================
     if (lane == 0) {
-      uint32_t qcnt = 0, kcnt = 0, vcnt = 0;
+      uint32_t qcnt = 0;
+      Ring<KST> kr;
+      Ring<VST> vr;
       bool ok = true;
       for (int w = blockIdx.x; w < a.num_items && ok; w += gridDim.x) {
         const Item it = decode_item(a, w);
@@ -180,23 +210,23 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
         for (int t = 0; t < 2; ++t)
 #pragma unroll
-          for (int cb = 0; cb < HD / 64; ++cb)
-            tma_load_2d(sQ + t * (TM * HD * 2) + cb * (TM * 128), &map_q, it.h * HD + cb * 64,
+          for (int cb = 0; cb < HD / EPB; ++cb)
+            tma_load_2d(sQ + t * (TM * HD * ESZ) + cb * (TM * 128), &map_q, it.h * HD + cb * EPB,
                         it.q0 + it.pair * 2 * TM + t * TM, bar_q_full);
         ++qcnt;
         const int hk = it.h / p.rep;
         for (int nb = it.ulo; nb < it.uhi; ++nb) {
           // K tile
           {
-            const uint32_t s = kcnt % KST;
-            ok = wait_or_abort(bar_k_empty + 8 * s, ((kcnt / KST) & 1) ^ 1, s_abort);
+            const uint32_t s = kr.slot;
+            ok = wait_or_abort(bar_k_empty + 8 * s, kr.phase ^ 1u, s_abort);
             if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
             mbar_expect_tx(bar_k_full + 8 * s, SM::kKStage);
             const uint32_t dst = sK + s * SM::kKStage;
             if (p.page_table == nullptr) {
 #pragma unroll
-              for (int cb = 0; cb < HD / 64; ++cb)
-                tma_load_2d(dst + cb * (TN * 128), &map_k, hk * HD + cb * 64, it.k0 + nb * TN, bar_k_full + 8 * s);
+              for (int cb = 0; cb < HD / EPB; ++cb)
+                tma_load_2d(dst + cb * (TN * 128), &map_k, hk * HD + cb * EPB, it.k0 + nb * TN, bar_k_full + 8 * s);
             } else {
               for (int r = 0; r < TN; r += a.kv_box_rows) {
                 const int kk = nb * TN + r;
@@ -206,23 +236,23 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
                   y = p.page_table[(int64_t)it.b * p.page_table_stride + lp] * p.page_size + (kk - lp * p.page_size);
                 }
 #pragma unroll
-                for (int cb = 0; cb < HD / 64; ++cb)
-                  tma_load_2d(dst + cb * (TN * 128) + r * 128, &map_k, hk * HD + cb * 64, y, bar_k_full + 8 * s);
+                for (int cb = 0; cb < HD / EPB; ++cb)
+                  tma_load_2d(dst + cb * (TN * 128) + r * 128, &map_k, hk * HD + cb * EPB, y, bar_k_full + 8 * s);
               }
             }
-            ++kcnt;
+            kr.advance();
           }
           // V tile
           {
-            const uint32_t s = vcnt % VST;
-            ok = wait_or_abort(bar_v_empty + 8 * s, ((vcnt / VST) & 1) ^ 1, s_abort);
+            const uint32_t s = vr.slot;
+            ok = wait_or_abort(bar_v_empty + 8 * s, vr.phase ^ 1u, s_abort);
             if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
             mbar_expect_tx(bar_v_full + 8 * s, SM::kVStage);
             const uint32_t dst = sV + s * SM::kVStage;
             if (p.page_table == nullptr) {
 #pragma unroll
-              for (int cb = 0; cb < HDV / 64; ++cb)
-                tma_load_2d(dst + cb * (TN * 128), &map_v, hk * HDV + cb * 64, it.k0 + nb * TN, bar_v_full + 8 * s);
+              for (int cb = 0; cb < HDV / EPB; ++cb)
+                tma_load_2d(dst + cb * (TN * 128), &map_v, hk * HDV + cb * EPB, it.k0 + nb * TN, bar_v_full + 8 * s);
             } else {
               for (int r = 0; r < TN; r += a.kv_box_rows) {
                 const int kk = nb * TN + r;
@@ -232,11 +262,11 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
                   y = p.page_table[(int64_t)it.b * p.page_table_stride + lp] * p.page_size + (kk - lp * p.page_size);
                 }
 #pragma unroll
-                for (int cb = 0; cb < HDV / 64; ++cb)
-                  tma_load_2d(dst + cb * (TN * 128) + r * 128, &map_v, hk * HDV + cb * 64, y, bar_v_full + 8 * s);
+                for (int cb = 0; cb < HDV / EPB; ++cb)
+                  tma_load_2d(dst + cb * (TN * 128) + r * 128, &map_v, hk * HDV + cb * EPB, y, bar_v_full + 8 * s);
               }
             }
-            ++vcnt;
+            vr.advance();
           }
         }
       }
@@ -244,41 +274,46 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       // drain: every copy this thread issued must have landed before the CTA may leave
       if (qcnt > 0) wait_or_abort(bar_q_full, (qcnt - 1) & 1, s_abort + 1 /* never set: pure time limit */);
       for (uint32_t s = 0; s < (uint32_t)KST; ++s) {
-        if (kcnt > s) { const uint32_t last = (kcnt - 1 - s) / KST; wait_or_abort(bar_k_full + 8 * s, last & 1, s_abort + 1); }
+        if (kr.n > s) { const uint32_t last = (kr.n - 1 - s) / KST; wait_or_abort(bar_k_full + 8 * s, last & 1, s_abort + 1); }
       }
       for (uint32_t s = 0; s < (uint32_t)VST; ++s) {
-        if (vcnt > s) { const uint32_t last = (vcnt - 1 - s) / VST; wait_or_abort(bar_v_full + 8 * s, last & 1, s_abort + 1); }
+        if (vr.n > s) { const uint32_t last = (vr.n - 1 - s) / VST; wait_or_abort(bar_v_full + 8 * s, last & 1, s_abort + 1); }
       }
     }
   } else if (warp == WARP_MMA) {
     // =========================================== MMA issuer =============================================
+    // operand format code: kind::f16 -> 1 = bf16, 0 = fp16; kind::f8f6f4 -> 0 = e4m3
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
+    constexpr int KB = 32;                       // bytes of the contraction dimension one MMA consumes
+    constexpr int KEL = KB / ESZ;                // ... in elements (16 for 16-bit, 32 for e4m3)
     constexpr uint32_t idesc_qk = umma_idesc(kFmt, TM, TN, false);
     constexpr uint32_t idesc_pv = umma_idesc(kFmt, TM, HDV, true);
     // ONE thread runs this role.  The tensor pipe accepts only a few instructions ahead, so everything this
     // thread does between two MMAs is time the pipe may idle: descriptors are built once and advanced by adds.
     if (lane == 0) {
-    uint32_t qcnt = 0, kcnt = 0, vcnt = 0, pcnt[2] = {0, 0}, oecnt[2] = {0, 0};
+    uint32_t qcnt = 0, pcnt[2] = {0, 0}, oecnt[2] = {0, 0};
+    Ring<KST> kr;
+    Ring<VST> vr;
     bool ok = true;
     constexpr bool leader = true;
     const uint64_t qd0 = umma_desc(sQ, 16, 1024), kd0 = umma_desc(sK, 16, 1024), vd0 = umma_desc(sV, TN * 128, 1024);
 
     auto issue_qk = [&](int t, uint32_t kslot) {
-      const uint64_t qd = qd0 + (uint64_t)(t * ((TM * HD * 2) >> 4));
+      const uint64_t qd = qd0 + (uint64_t)(t * ((TM * HD * ESZ) >> 4));
       const uint64_t kd = kd0 + (uint64_t)(kslot * (SM::kKStage >> 4));
 #pragma unroll
-      for (int ks = 0; ks < HD / 16; ++ks) {
+      for (int ks = 0; ks < HD / KEL; ++ks) {
         constexpr int kBlk = (TM * 128) >> 4;
-        const uint64_t off = (uint64_t)((ks >> 2) * kBlk + (ks & 3) * 2);
-        umma_ss<false>(tmem + t * TN, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+        const uint64_t off = (uint64_t)((ks >> 2) * kBlk + (ks & 3) * 2);   // 4 steps of 32 bytes per 128-byte row
+        umma_ss<F8>(tmem + t * TN, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
       }
       umma_commit(bar_s_full + 8 * t);
     };
     auto issue_pv = [&](int t, uint32_t vslot, bool first) {
       const uint64_t vd = vd0 + (uint64_t)(vslot * (SM::kVStage >> 4));
 #pragma unroll
-      for (int ks = 0; ks < TN / 16; ++ks)
-        umma_ts<false>(tmem + 256 + t * 128, tmem + t * TN + ks * 8, vd + (uint64_t)(ks * 128), idesc_pv,
+      for (int ks = 0; ks < TN / KEL; ++ks)   // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
+        umma_ts<F8>(tmem + 256 + t * 128, tmem + t * TN + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
                        (!first || ks > 0) ? 1u : 0u);
     };
 
@@ -290,21 +325,21 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
       // prologue: QK of the first block
       {
-        const uint32_t ks = kcnt % KST;
-        ok = wait_or_abort(bar_k_full + 8 * ks, (kcnt / KST) & 1, s_abort);
+        const uint32_t ks = kr.slot;
+        ok = wait_or_abort(bar_k_full + 8 * ks, kr.phase, s_abort);
         if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
         tc_fence_after_sync();
 #pragma unroll
         for (int t = 0; t < 2; ++t)
           if (it.ulo >= it.lo[t] && it.ulo < it.hi[t]) issue_qk(t, ks);
         if (leader) umma_commit(bar_k_empty + 8 * ks);
-        ++kcnt;
+        kr.advance();
       }
       for (int i = it.ulo; i < it.uhi && ok; ++i) {
         const bool nxt = i + 1 < it.uhi;
-        const uint32_t vs = vcnt % VST;
-        const uint32_t ks = kcnt % KST;       // slot of block i+1 (if any)
-        ok = wait_or_abort(bar_v_full + 8 * vs, (vcnt / VST) & 1, s_abort);
+        const uint32_t vs = vr.slot;
+        const uint32_t ks = kr.slot;          // slot of block i+1 (if any)
+        ok = wait_or_abort(bar_v_full + 8 * vs, vr.phase, s_abort);
         if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
         bool k_ready = false;
 #pragma unroll
@@ -325,7 +360,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           }
           if (nxt && i + 1 >= it.lo[t] && i + 1 < it.hi[t]) {
             if (!k_ready) {
-              ok = wait_or_abort(bar_k_full + 8 * ks, (kcnt / KST) & 1, s_abort);
+              ok = wait_or_abort(bar_k_full + 8 * ks, kr.phase, s_abort);
               if (!ok) break;
               tc_fence_after_sync();
               k_ready = true;
@@ -335,14 +370,14 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         }
         if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
         if (leader) umma_commit(bar_v_empty + 8 * vs);
-        ++vcnt;
+        vr.advance();
         if (nxt) {
           if (!k_ready) {   // block i+1 belongs to neither tile: still consume its K slot
-            ok = wait_or_abort(bar_k_full + 8 * ks, (kcnt / KST) & 1, s_abort);
+            ok = wait_or_abort(bar_k_full + 8 * ks, kr.phase, s_abort);
             if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
           }
           if (leader) umma_commit(bar_k_empty + 8 * ks);
-          ++kcnt;
+          kr.advance();
         }
       }
       if (ok && leader) umma_commit(bar_q_empty);
@@ -394,6 +429,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       if (p.window_left >= 0) lo_max = max(lo_max, qp_last - p.window_left);
 
       float m_used = -INFINITY, l = 0.f;
+      float lr = 0.f;   // e4m3 only: sum of the ROUNDED probabilities (normalises O); l stays exact for the LSE
       for (int i = it.lo[t]; i < it.hi[t]; ++i) {
         ok = wait_or_abort(bar_s_full + 8 * t, scnt & 1, s_abort);
         ++scnt;
@@ -444,6 +480,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           corr = ex2(m_used - y_max);
           m_used = y_max;
           l *= corr;
+          lr *= corr;
           rescale = true;
         }
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
@@ -451,15 +488,37 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         const float2 c2 = make_float2(c_mul, c_mul), nm2 = make_float2(neg_m, neg_m);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
+          if constexpr (!F8) {
+            uint32_t pk[16];
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const float2 y = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
-            const float2 pp = make_float2(ex2(y.x), ex2(y.y));
-            psum[(j >> 1) & 3] = fadd2(psum[(j >> 1) & 3], pp);
-            pk[j >> 1] = pack2<T>(pp.x, pp.y);
+            for (int j = 0; j < 32; j += 2) {
+              const float2 y = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
+              const float2 pp = make_float2(ex2(y.x), ex2(y.y));
+              psum[(j >> 1) & 3] = fadd2(psum[(j >> 1) & 3], pp);
+              pk[j >> 1] = pack2<TO>(pp.x, pp.y);
+            }
+            tmem_st16(tS + c * 16, pk);
+          } else {
+            // four e4m3 probabilities per TMEM column.  The row sum is taken over the ROUNDED probabilities, so
+            // that numerator (P V on the tensor cores) and denominator describe the same weights.
+            uint32_t pk[8];
+            __half2 hs[4] = {__half2(), __half2(), __half2(), __half2()};
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              const float2 y0 = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
+              const float2 y1 = ffma2(make_float2(__uint_as_float(sreg[c][j + 2]), __uint_as_float(sreg[c][j + 3])), c2, nm2);
+              const float2 p0 = make_float2(ex2(y0.x), ex2(y0.y)), p1 = make_float2(ex2(y1.x), ex2(y1.y));
+              psum[(j >> 2) & 3] = fadd2(psum[(j >> 2) & 3], fadd2(p0, p1));
+              const uint32_t q4 = pack4_e4m3(p0.x, p0.y, p1.x, p1.y);
+              pk[j >> 2] = q4;
+              const uint32_t h0 = e4m3x2_to_f16x2((uint16_t)(q4 & 0xffffu)), h1 = e4m3x2_to_f16x2((uint16_t)(q4 >> 16));
+              hs[(j >> 2) & 3] = __hadd2(hs[(j >> 2) & 3],
+                                         __hadd2(*reinterpret_cast<const __half2*>(&h0), *reinterpret_cast<const __half2*>(&h1)));
+            }
+            tmem_st8(tS + c * 8, pk);
+            const float2 f01 = __half22float2(__hadd2(hs[0], hs[1])), f23 = __half22float2(__hadd2(hs[2], hs[3]));
+            lr += (f01.x + f23.x) + (f01.y + f23.y);
           }
-          tmem_st16(tS + c * 16, pk);
         }
         {
           const float2 s01 = fadd2(psum[0], psum[1]), s23 = fadd2(psum[2], psum[3]);
@@ -494,16 +553,19 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         tc_fence_after_sync();
       }
       float m_fin = m_used, l_fin = l, osc = 1.f;
+      float l_norm = F8 ? lr : l;          // what O is divided by
       if (p.s_aux) {
         const float ys = p.s_aux[it.h] * kLog2e;
         const float mn = fmaxf(m_used, ys);
         osc = (m_used == -INFINITY) ? 0.f : ex2(m_used - mn);
-        l_fin = l * osc + ex2(ys - mn);
+        const float sink = ex2(ys - mn);
+        l_fin = l * osc + sink;
+        l_norm = l_norm * osc + sink;
         m_fin = mn;
       }
-      const float inv = l_fin > 0.f ? osc * vds / l_fin : 0.f;
+      const float inv = l_norm > 0.f ? osc * vds / l_norm : 0.f;
       const bool row_ok = row < it.seqlen_q;
-      T* op = reinterpret_cast<T*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
+      TO* op = reinterpret_cast<TO*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
 #pragma unroll 1
       for (int c = 0; c < HDV / 32; ++c) {
         uint32_t o[32];
@@ -518,10 +580,10 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
           for (int j = 0; j < 32; j += 8) {
             uint4 v;
-            v.x = pack2<T>(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
-            v.y = pack2<T>(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
-            v.z = pack2<T>(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
-            v.w = pack2<T>(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
+            v.x = pack2<TO>(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
+            v.y = pack2<TO>(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+            v.z = pack2<TO>(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+            v.w = pack2<TO>(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
             *reinterpret_cast<uint4*>(op + c * 32 + j) = v;
           }
         }
@@ -568,10 +630,13 @@ static bool make_map_2d(CUtensorMap* m, const void* ptr, int dtype, uint64_t row
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {pitch_elems * 2};
-  const cuuint32_t box[2] = {64, box_rows};
+  const uint32_t esz = dtype == FA_DT_FP8_E4M3 ? 1 : 2;
+  const cuuint64_t strides[1] = {pitch_elems * esz};
+  const cuuint32_t box[2] = {128 / esz, box_rows};
   const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapDataType dt = dtype == FA_DT_FP16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType dt = dtype == FA_DT_FP8_E4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : dtype == FA_DT_FP16   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                         : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   return fn(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
@@ -579,7 +644,7 @@ static bool make_map_2d(CUtensorMap* m, const void* ptr, int dtype, uint64_t row
 
 template <typename T, int HD, int HDV, int KST, int VST>
 static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_rows, cudaStream_t stream) {
-  using SM = Smem<HD, HDV, KST, VST>;
+  using SM = Smem<Elem<T>::kSize, HD, HDV, KST, VST>;
   TcArgs a;
   a.kp = kp;
   a.max_pairs = (kp.max_seqlen_q + 2 * TM - 1) / (2 * TM);
@@ -607,9 +672,10 @@ static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
 // Shapes the tensor-core prefill route takes. Layout conditions (heads back to back inside a row, pages
 // back to back) are checked at launch: fa_b200_fwd re-plans onto the general route when they do not hold.
 bool prefill_tc_supported(const PlanInput& in) {
-  if (in.q_dtype != in.kv_dtype || in.q_dtype == FA_DT_FP8_E4M3) return false;
+  if (in.q_dtype != in.kv_dtype) return false;
   const bool hd_ok = (in.hd == 64 && in.hdv == 64) || (in.hd == 128 && in.hdv == 128) || (in.hd == 192 && in.hdv == 128);
   if (!hd_ok) return false;
+  if (in.q_dtype == FA_DT_FP8_E4M3 && !(in.hd == 128 && in.hdv == 128)) return false;   // e4m3: head_dim 128 only
   if (in.page_size > 0) {
     const int ps = in.page_size;
     if (ps % 8 != 0 || !((128 % ps == 0) || (ps % 128 == 0))) return false;
@@ -631,6 +697,8 @@ bool prefill_tc_layout_ok(const FaFwdParams* p) {
 int launch_prefill_tc(const KParams& kp, const Plan& pl, int dtype, cudaStream_t stream) {
   const uint64_t kv_rows = kp.page_table ? (uint64_t)kp.num_pages * (uint64_t)kp.page_size : (uint64_t)kp.total_k;
   const bool bf = dtype != FA_DT_FP16;
+  if (kp.q_fp8 && kp.kv_fp8)
+    return kp.hd == 128 && kp.hdv == 128 ? tc::launch_impl<tc::fp8_t, 128, 128, 4, 4>(kp, pl, FA_DT_FP8_E4M3, kv_rows, stream) : -1;
   if (kp.hd == 128 && kp.hdv == 128)
     return bf ? tc::launch_impl<__nv_bfloat16, 128, 128, 2, 2>(kp, pl, dtype, kv_rows, stream)
               : tc::launch_impl<__half, 128, 128, 2, 2>(kp, pl, dtype, kv_rows, stream);

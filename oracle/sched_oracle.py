@@ -77,9 +77,11 @@ class Plan:
 
 
 def prefill_tc_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> bool:
-    if q_dtype != kv_dtype or q_dtype == DT_FP8:
+    if q_dtype != kv_dtype:
         return False
     if (hd, hdv) not in ((64, 64), (128, 128), (192, 128)):
+        return False
+    if q_dtype == DT_FP8 and (hd, hdv) != (128, 128):
         return False
     if page_size and not (page_size % 8 == 0 and (128 % page_size == 0 or page_size % 128 == 0)):
         return False
