@@ -7,6 +7,8 @@
 //   warp  8    MMA issuer: S_t = Q_t K^T (operands in shared memory), O_t += P_t V (P in TMEM)
 //   warp  9    TMA producer: Q pair, K ring, V ring (no cluster multicast: each CTA loads its own tiles)
 //   warps 10-11 idle (they complete the third warpgroup so that register tiers can be set per warpgroup)
+// Work items (256 query rows of one (batch, head); late = heavy tiles first) are handed out through one global
+// atomic counter and a two-slot mailbox in shared memory, so SMs that finish early take more.
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t overlays the first 64
 // columns of S_t once the owning thread has read its S row.
 // The tensor pipe runs [PV0(i), QK0(i+1), PV1(i), QK1(i+1)] so that one tile's softmax overlaps the other
@@ -64,8 +66,8 @@ struct Smem {
   static constexpr int kKStage = TN * HD * ESZ;
   static constexpr int kVStage = TN * HDV * ESZ;
   static constexpr int kBarOff = kQBytes + KST * kKStage + VST * kVStage;
-  static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1;
-  static constexpr int kBytes = kBarOff + kNumBars * 8 + 16;
+  static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1 + 4;
+  static constexpr int kBytes = kBarOff + kNumBars * 8 + 32;   // + abort flags, TMEM base, two work-id slots
 };
 
 // All roles derive the same tile geometry from the same inputs.
@@ -165,6 +167,9 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   const uint32_t bar_o_full = bar_p_full + 16;           // [2]
   const uint32_t bar_o_empty = bar_o_full + 16;          // [2]
   const uint32_t bar_drain = bar_o_empty + 16;           // MMA warp's private drain barrier
+  const uint32_t bar_w_full = bar_drain + 8;             // [2] work id published by the TMA thread
+  const uint32_t bar_w_empty = bar_w_full + 16;          // [2] read by the MMA thread and the 8 softmax warps
+  volatile int* s_work = reinterpret_cast<volatile int*>(sm + SM::kBarOff + SM::kNumBars * 8 + 16);
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + SM::kBarOff + SM::kNumBars * 8);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sm + SM::kBarOff + SM::kNumBars * 8 + 8);
 
@@ -179,6 +184,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       mbar_init(bar_o_full + 8 * t, 1); mbar_init(bar_o_empty + 8 * t, 4);
     }
     mbar_init(bar_drain, 1);
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_w_full + 8 * i, 1); mbar_init(bar_w_empty + 8 * i, 9); }
     s_abort[0] = 0;
     s_abort[1] = 0;   // [1] is never raised: waits that may only end by completion or time limit
     mbar_fence_init();
@@ -201,7 +207,25 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       Ring<KST> kr;
       Ring<VST> vr;
       bool ok = true;
-      for (int w = blockIdx.x; w < a.num_items && ok; w += gridDim.x) {
+      uint32_t wcnt = 0;
+      // work items are handed out heaviest first through one global counter; every role of this CTA learns the
+      // id from a two-slot mailbox in shared memory
+      auto fetch_and_publish = [&]() -> int {
+        const uint32_t slot = wcnt & 1;
+        if (!wait_or_abort(bar_w_empty + 8 * slot, ((wcnt >> 1) & 1) ^ 1, s_abort)) {
+          report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA);
+          ok = false;
+          return 0x7fffffff;
+        }
+        const int w = atomicAdd(p.counters, 1);
+        s_work[slot] = w;
+        mbar_arrive(bar_w_full + 8 * slot);
+        ++wcnt;
+        return w;
+      };
+      int w_next = fetch_and_publish();
+      for (int w = w_next; w < a.num_items && ok; w = w_next) {
+        w_next = fetch_and_publish();   // one item ahead: the counter's round trip hides behind this item's loads
         const Item it = decode_item(a, w);
         if (!it.valid || it.uhi <= it.ulo) continue;
         ok = wait_or_abort(bar_q_empty, (qcnt & 1) ^ 1, s_abort);
@@ -317,7 +341,16 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
                        (!first || ks > 0) ? 1u : 0u);
     };
 
-    for (int w = blockIdx.x; w < a.num_items && ok; w += gridDim.x) {
+    uint32_t wcnt = 0;
+    auto next_work = [&]() -> int {
+      const uint32_t slot = wcnt & 1;
+      if (!wait_or_abort(bar_w_full + 8 * slot, (wcnt >> 1) & 1, s_abort)) { ok = false; return 0x7fffffff; }
+      const int w = s_work[slot];
+      mbar_arrive(bar_w_empty + 8 * slot);
+      ++wcnt;
+      return w;
+    };
+    for (int w = next_work(); w < a.num_items && ok; w = next_work()) {
       const Item it = decode_item(a, w);
       if (!it.valid || it.uhi <= it.ulo) continue;
       ok = wait_or_abort(bar_q_full, qcnt & 1, s_abort);
@@ -400,7 +433,17 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     uint32_t scnt = 0, ocnt = 0;
     bool ok = true;
 
-    for (int w = blockIdx.x; w < a.num_items && ok; w += gridDim.x) {
+    uint32_t wcnt = 0;
+    auto next_work = [&]() -> int {
+      const uint32_t slot = wcnt & 1;
+      if (!wait_or_abort(bar_w_full + 8 * slot, (wcnt >> 1) & 1, s_abort)) { ok = false; return 0x7fffffff; }
+      const int w = s_work[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_w_empty + 8 * slot);
+      ++wcnt;
+      return w;
+    };
+    for (int w = next_work(); w < a.num_items && ok; w = next_work()) {
       const Item it = decode_item(a, w);
       if (!it.valid) continue;
       const int row0 = it.pair * 2 * TM + t * TM;
