@@ -242,11 +242,10 @@ def run_ours(args) -> None:
         e2e = {"value": flops * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": _tensor_bytes(h_out)}
 
-    # ---- decode workload (secondary object) ----
-    decode = None
-    if not args.no_decode:
+    # ---- decode workload (secondary objects: bf16 KV cache, and e4m3 KV cache with --decode-fp8) ----
+    def decode_leg(kv_dtype):
         try:
-            dhost = W.paged_decode(seed=rank)
+            dhost = W.paged_decode(seed=rank, kv_dtype=kv_dtype)
             kvb = dhost.kv_bytes()
             dp = dhost.to(dev)
             dout = torch.empty(dp.q.shape[0], dp.q.shape[1], dp.v.shape[-1], device=dev, dtype=torch.bfloat16)
@@ -259,8 +258,9 @@ def run_ours(args) -> None:
                 dstep(i)
             dms = _time_steps(dstep, max(3, min(args.steps, 100)), dist, world)
             gbs = kvb / (dms * 1e-3) / 1e9
-            decode = {
-                "metric": "paged decode HBM GB/s (B=128 q_len=1 ctx 1k..32k page 64 Hq=32 Hkv=8 d=128 bf16 KV, leftpad 0..63)",
+            return {
+                "metric": f"paged decode HBM GB/s (B=128 q_len=1 ctx 1k..32k page 64 Hq=32 Hkv=8 d=128 {kv_dtype} KV, "
+                          "leftpad 0..63)",
                 "value": gbs * world, "unit": "GB/s", "ms_per_step": dms, "kv_bytes_per_step": kvb,
                 "num_splits": nspl,
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -268,7 +268,10 @@ def run_ours(args) -> None:
                 "l2": f"KV pool ({kvb / 1e9:.2f} GB) larger than L2",
             }
         except Exception as e:  # reported, never hidden
-            decode = {"error": repr(e)}
+            return {"error": repr(e)}
+
+    decode = None if args.no_decode else decode_leg("bf16")
+    decode_fp8 = decode_leg("fp8") if args.decode_fp8 else None
 
     if rank != 0:
         if world > 1:
@@ -287,7 +290,7 @@ def run_ours(args) -> None:
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": per_gpu / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
                      "kernel": "fwd_prefill_tc_kernel", "launch_ms": ms},
-        "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks, "decode": decode, "cpu_baseline": cpu,
+        "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks, "decode": decode, "decode_fp8": decode_fp8, "cpu_baseline": cpu,
         "kernels_per_step": {"prefill": ["fwd_prefill_tc_kernel"], "decode": ["sched_kernel", "fwd_decode_kernel"]},
     }
     print(json.dumps(line))
@@ -358,6 +361,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-decode", action="store_true", help="skip the decode workload")
+    ap.add_argument("--decode-fp8", action="store_true", help="also time the decode workload with an e4m3 KV cache")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--batch", type=int, default=4, help="prefill batch per GPU (4 = the benchmark configuration; "
