@@ -245,9 +245,8 @@ def run_ours(args) -> None:
     # ---- decode workload (secondary objects: bf16 KV cache, and e4m3 KV cache with --decode-fp8) ----
     def decode_leg(kv_dtype):
         try:
-            dhost = W.paged_decode(seed=rank, kv_dtype=kv_dtype)
-            kvb = dhost.kv_bytes()
-            dp = dhost.to(dev)
+            dp = W.paged_decode_on_device(dev, seed=rank, kv_dtype=kv_dtype)   # the 8.5 GB pool is drawn on the GPU
+            kvb = dp.kv_bytes()
             dout = torch.empty(dp.q.shape[0], dp.q.shape[1], dp.v.shape[-1], device=dev, dtype=torch.bfloat16)
             nspl = capi.num_splits(dp.q, dp.k, dp.v, **dp.capi_kw())
 

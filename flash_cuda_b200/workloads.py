@@ -248,6 +248,59 @@ def paged_decode(seed: int = 0, B: int = 128, ctx_lo: int = 1024, ctx_hi: int = 
                         page_size=page_size, leftpad=pad, seed=seed + 1)
 
 
+def paged_decode_on_device(device, seed: int = 0, B: int = 128, ctx_lo: int = 1024, ctx_hi: int = 32768,
+                           kv_dtype: str = "bf16", page_size: int = 64) -> Problem:
+    """The paged-decode configuration with the KV pool drawn ON THE DEVICE (the pool is 8.5 GB in bf16; drawing
+    it on the host costs 17 GB of fp32 per process, too much when 8 ranks share one host).  Lengths, leftpad and
+    the page permutation are the same seeded host draws as `paged_decode`; K/V/Q values come from the device
+    generator.  Returns a Problem whose tensors already live on `device`."""
+    g = torch.Generator().manual_seed(seed)
+    ctx = [int(c) for c in torch.randint(ctx_lo, ctx_hi + 1, (B,), generator=g).tolist()]
+    pad = torch.randint(0, 64, (B,), generator=g).tolist()
+    pad = [min(int(p), c - 1) for p, c in zip(pad, ctx)]
+    g2 = torch.Generator().manual_seed(seed + 1)
+    hq, hkv, hd = 32, 8, 128
+    npages = [(c + page_size - 1) // page_size for c in ctx]
+    total_pages = sum(npages) + 3
+    perm = torch.randperm(total_pages, generator=g2)
+    page_table = torch.zeros(B, max(npages), dtype=torch.int32)
+    o = 0
+    for i, n in enumerate(npages):
+        page_table[i, :n] = perm[o:o + n].to(torch.int32)
+        o += n
+    gd = torch.Generator(device=device).manual_seed(seed * 104729 + 7)
+    q = torch.randn(B, hq, hd, generator=gd, device=device, dtype=torch.float32).to(torch.bfloat16)
+    k = torch.empty(total_pages, page_size, hkv, hd, device=device, dtype=torch.bfloat16)
+    v = torch.empty_like(k)
+    for p0 in range(0, total_pages, 2048):
+        p1 = min(total_pages, p0 + 2048)
+        k[p0:p1] = torch.randn(p1 - p0, page_size, hkv, hd, generator=gd, device=device, dtype=torch.bfloat16)
+        v[p0:p1] = torch.randn(p1 - p0, page_size, hkv, hd, generator=gd, device=device, dtype=torch.bfloat16)
+    kd = vd = None
+    pt_dev = page_table.to(device)
+    if kv_dtype == "fp8":
+        k8 = torch.empty(k.shape, device=device, dtype=torch.float8_e4m3fn)
+        v8 = torch.empty_like(k8)
+        k8.copy_((k.float() / 0.01).clamp(-448, 448))      # pages no sequence owns: any finite value
+        v8.copy_((v.float() / 0.01).clamp(-448, 448))
+        kd = torch.empty(B, hkv, device=device, dtype=torch.float32)
+        vd = torch.empty_like(kd)
+        for b in range(B):
+            rows = pt_dev[b, :npages[b]].long()
+            for src, dst, dsc in ((k, k8, kd), (v, v8, vd)):
+                xb = src[rows].float()
+                d = (xb.abs().amax(dim=(0, 1, 3)) / 448.0).clamp_min(1e-8)
+                dsc[b] = d
+                dst[rows] = (xb / d.view(1, 1, hkv, 1)).to(torch.float8_e4m3fn)
+        k, v = k8, v8
+    return Problem(name=f"paged_decode_{kv_dtype}_b{B}", q=q, k=k, v=v,
+                   cu_seqlens_q=torch.arange(B + 1, device=device, dtype=torch.int32), cu_seqlens_k=None,
+                   seqused_k=torch.tensor(ctx, device=device, dtype=torch.int32), page_table=pt_dev,
+                   leftpad_k=torch.tensor(pad, device=device, dtype=torch.int32), q_descale=None, k_descale=kd,
+                   v_descale=vd, s_aux=None, max_seqlen_q=1, max_seqlen_k=max(ctx), softmax_scale=hd ** -0.5,
+                   causal=True, q_lens=[1] * B, k_lens=ctx)
+
+
 def long_context(device, seed: int = 0, q_len: int = 4096, k_len: int = 524288, heads: int = 128, hd: int = 192,
                  hdv: int = 128, page_size: int = 64, k_begin: int = 0, k_end: Optional[int] = None) -> Problem:
     """Long-context prefill: B=1, a chunk of q_len query rows against a paged KV of k_len tokens, Hq=Hkv=heads,
