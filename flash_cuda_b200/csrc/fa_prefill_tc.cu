@@ -306,120 +306,133 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     }
   } else if (warp == WARP_MMA) {
     // =========================================== MMA issuer =============================================
+    // The WHOLE warp runs this role's control flow, and every value that steers it (work id, block ranges,
+    // ring positions, TMEM base) is made warp-uniform by construction (broadcast from lane 0, votes), so the
+    // compiler can keep descriptors and addresses in uniform registers, which is where the MMA instruction
+    // takes its operands from.  Only the tcgen05 instructions themselves and barrier arrivals sit behind
+    // `elect_one()`.  (With the role under `if (lane == 0)` the same code measured ~1900 cycles of thread
+    // time per key block beside the 2240 the tensor pipe needs: every MMA paid for moving five operands from
+    // per-thread to uniform registers.)
     // operand format code: kind::f16 -> 1 = bf16, 0 = fp16; kind::f8f6f4 -> 0 = e4m3
     constexpr uint32_t kFmt = std::is_same<T, __nv_bfloat16>::value ? 1u : 0u;
     constexpr int KB = 32;                       // bytes of the contraction dimension one MMA consumes
     constexpr int KEL = KB / ESZ;                // ... in elements (16 for 16-bit, 32 for e4m3)
     constexpr uint32_t idesc_qk = umma_idesc(kFmt, TM, TN, false);
     constexpr uint32_t idesc_pv = umma_idesc(kFmt, TM, HDV, true);
-    // ONE thread runs this role.  The tensor pipe accepts only a few instructions ahead, so everything this
-    // thread does between two MMAs is time the pipe may idle: descriptors are built once and advanced by adds.
-    if (lane == 0) {
+    constexpr uint32_t FULL = 0xffffffffu;
+    const uint32_t tmem_u = __shfl_sync(FULL, tmem, 0);
     uint32_t qcnt = 0, pcnt[2] = {0, 0}, oecnt[2] = {0, 0};
     Ring<KST> kr;
     Ring<VST> vr;
-    bool ok = true;
-    constexpr bool leader = true;
+    // A wait that runs out does not branch out of the loops (that would make every loop-carried value
+    // lane-dependent): it raises the CTA's abort flag, later waits of this lane return at once, the MMAs of
+    // the current item are still issued (on whatever the buffers hold; nothing faults) and the work loop ends
+    // at the next item boundary through a vote.
+    bool fail = false;
+    auto wait = [&](uint32_t bar, uint32_t parity) {
+      if (!fail && !wait_or_abort(bar, parity, s_abort)) {
+        fail = true;
+        report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA);
+        *s_abort = 1;
+      }
+    };
     const uint64_t qd0 = umma_desc(sQ, 16, 1024), kd0 = umma_desc(sK, 16, 1024), vd0 = umma_desc(sV, TN * 128, 1024);
 
     auto issue_qk = [&](int t, uint32_t kslot) {
       const uint64_t qd = qd0 + (uint64_t)(t * ((TM * HD * ESZ) >> 4));
       const uint64_t kd = kd0 + (uint64_t)(kslot * (SM::kKStage >> 4));
+      if (elect_one()) {
 #pragma unroll
-      for (int ks = 0; ks < HD / KEL; ++ks) {
-        constexpr int kBlk = (TM * 128) >> 4;
-        const uint64_t off = (uint64_t)((ks >> 2) * kBlk + (ks & 3) * 2);   // 4 steps of 32 bytes per 128-byte row
-        umma_ss<F8>(tmem + t * TN, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+        for (int ks = 0; ks < HD / KEL; ++ks) {
+          constexpr int kBlk = (TM * 128) >> 4;
+          const uint64_t off = (uint64_t)((ks >> 2) * kBlk + (ks & 3) * 2);   // 4 steps of 32 bytes per 128-byte row
+          umma_ss<F8>(tmem_u + t * TN, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(bar_s_full + 8 * t);
       }
-      umma_commit(bar_s_full + 8 * t);
     };
     auto issue_pv = [&](int t, uint32_t vslot, bool first) {
       const uint64_t vd = vd0 + (uint64_t)(vslot * (SM::kVStage >> 4));
+      if (elect_one()) {
 #pragma unroll
-      for (int ks = 0; ks < TN / KEL; ++ks)   // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
-        umma_ts<F8>(tmem + 256 + t * 128, tmem + t * TN + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
-                       (!first || ks > 0) ? 1u : 0u);
+        for (int ks = 0; ks < TN / KEL; ++ks)   // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
+          umma_ts<F8>(tmem_u + 256 + t * 128, tmem_u + t * TN + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
+                      (!first || ks > 0) ? 1u : 0u);
+      }
     };
+    auto commit = [&](uint32_t bar) { if (elect_one()) umma_commit(bar); };
 
     uint32_t wcnt = 0;
-    auto next_work = [&]() -> int {
+    while (true) {
       const uint32_t slot = wcnt & 1;
-      if (!wait_or_abort(bar_w_full + 8 * slot, (wcnt >> 1) & 1, s_abort)) { ok = false; return 0x7fffffff; }
-      const int w = s_work[slot];
-      mbar_arrive(bar_w_empty + 8 * slot);
+      wait(bar_w_full + 8 * slot, (wcnt >> 1) & 1);
+      const int w = __shfl_sync(FULL, s_work[slot], 0);
+      if (elect_one()) mbar_arrive(bar_w_empty + 8 * slot);
       ++wcnt;
-      return w;
-    };
-    for (int w = next_work(); w < a.num_items && ok; w = next_work()) {
-      const Item it = decode_item(a, w);
-      if (!it.valid || it.uhi <= it.ulo) continue;
-      ok = wait_or_abort(bar_q_full, qcnt & 1, s_abort);
+      if (__any_sync(FULL, fail) || w >= a.num_items) break;
+      const Item it0 = decode_item(a, w);
+      // block ranges, broadcast so that every loop bound below is warp-uniform
+      const int lo0 = __shfl_sync(FULL, it0.lo[0], 0), hi0 = __shfl_sync(FULL, it0.hi[0], 0);
+      const int lo1 = __shfl_sync(FULL, it0.lo[1], 0), hi1 = __shfl_sync(FULL, it0.hi[1], 0);
+      const int ulo = __shfl_sync(FULL, it0.ulo, 0), uhi = __shfl_sync(FULL, it0.uhi, 0);
+      const int valid = __shfl_sync(FULL, (int)it0.valid, 0);
+      if (!valid || uhi <= ulo) continue;
+      const int lo[2] = {lo0, lo1}, hi[2] = {hi0, hi1};
+      wait(bar_q_full, qcnt & 1);
       ++qcnt;
-      if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
       // prologue: QK of the first block
       {
         const uint32_t ks = kr.slot;
-        ok = wait_or_abort(bar_k_full + 8 * ks, kr.phase, s_abort);
-        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
+        wait(bar_k_full + 8 * ks, kr.phase);
         tc_fence_after_sync();
 #pragma unroll
         for (int t = 0; t < 2; ++t)
-          if (it.ulo >= it.lo[t] && it.ulo < it.hi[t]) issue_qk(t, ks);
-        if (leader) umma_commit(bar_k_empty + 8 * ks);
+          if (ulo >= lo[t] && ulo < hi[t]) issue_qk(t, ks);
+        commit(bar_k_empty + 8 * ks);
         kr.advance();
       }
-      for (int i = it.ulo; i < it.uhi && ok; ++i) {
-        const bool nxt = i + 1 < it.uhi;
+      for (int i = ulo; i < uhi; ++i) {
+        const bool nxt = i + 1 < uhi;
         const uint32_t vs = vr.slot;
         const uint32_t ks = kr.slot;          // slot of block i+1 (if any)
-        ok = wait_or_abort(bar_v_full + 8 * vs, vr.phase, s_abort);
-        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
+        wait(bar_v_full + 8 * vs, vr.phase);
         bool k_ready = false;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
-          if (i >= it.lo[t] && i < it.hi[t]) {
-            const bool first = i == it.lo[t];
+          if (i >= lo[t] && i < hi[t]) {
+            const bool first = i == lo[t];
             if (first) {   // O_t is overwritten: the previous item's epilogue must have read it
-              ok = wait_or_abort(bar_o_empty + 8 * t, (oecnt[t] & 1) ^ 1, s_abort);
+              wait(bar_o_empty + 8 * t, (oecnt[t] & 1) ^ 1);
               ++oecnt[t];
-              if (!ok) break;
             }
-            ok = wait_or_abort(bar_p_full + 8 * t, pcnt[t] & 1, s_abort);
+            wait(bar_p_full + 8 * t, pcnt[t] & 1);
             ++pcnt[t];
-            if (!ok) break;
             tc_fence_after_sync();
             issue_pv(t, vs, first);
-            if (i + 1 == it.hi[t] && leader) umma_commit(bar_o_full + 8 * t);
+            if (i + 1 == hi[t]) commit(bar_o_full + 8 * t);
           }
-          if (nxt && i + 1 >= it.lo[t] && i + 1 < it.hi[t]) {
+          if (nxt && i + 1 >= lo[t] && i + 1 < hi[t]) {
             if (!k_ready) {
-              ok = wait_or_abort(bar_k_full + 8 * ks, kr.phase, s_abort);
-              if (!ok) break;
+              wait(bar_k_full + 8 * ks, kr.phase);
               tc_fence_after_sync();
               k_ready = true;
             }
             issue_qk(t, ks);
           }
         }
-        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
-        if (leader) umma_commit(bar_v_empty + 8 * vs);
+        commit(bar_v_empty + 8 * vs);
         vr.advance();
         if (nxt) {
-          if (!k_ready) {   // block i+1 belongs to neither tile: still consume its K slot
-            ok = wait_or_abort(bar_k_full + 8 * ks, kr.phase, s_abort);
-            if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA); break; }
-          }
-          if (leader) umma_commit(bar_k_empty + 8 * ks);
+          if (!k_ready) wait(bar_k_full + 8 * ks, kr.phase);   // block i+1 belongs to neither tile: still consume its K slot
+          commit(bar_k_empty + 8 * ks);
           kr.advance();
         }
       }
-      if (ok && leader) umma_commit(bar_q_empty);
+      commit(bar_q_empty);
     }
-    if (!ok) *s_abort = 1;
     // drain: all MMAs this warp issued must have retired before TMEM is released
-    umma_commit(bar_drain);
+    commit(bar_drain);
     wait_or_abort(bar_drain, 0, s_abort + 1);
-    }
   }
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");

@@ -65,6 +65,14 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
   return false;
 }
 
+// One lane of the (fully converged) warp, the same lane every time: gates instructions that ONE thread must issue
+// while the warp's control flow stays uniform.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred P;\n elect.sync _|P, 0xffffffff;\n selp.u32 %0, 1, 0, P;\n}" : "=r"(pred));
+  return pred != 0;
+}
+
 // ----------------------------------------------------------------------------------------------
 // fences
 // ----------------------------------------------------------------------------------------------
