@@ -37,6 +37,15 @@ constexpr int WARP_MMA = 8, WARP_TMA = 9;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
+// experiment knobs
+#ifndef FA_TC_EMU
+#define FA_TC_EMU 0        // of every 4 column pairs, how many take 2^x on the FMA pipe instead of the SFU
+#endif
+#ifndef FA_TC_PSPLIT
+#define FA_TC_PSPLIT 0     // P is handed to the MMA thread in two parts: the first 96 keys, then the last 32
+#endif
+constexpr int kEmuPairs = FA_TC_EMU;
+constexpr bool kPSplit = FA_TC_PSPLIT != 0;
 enum Role : unsigned { ROLE_TMA = 1, ROLE_MMA = 2, ROLE_SOFTMAX = 3, ROLE_EPILOGUE = 4 };
 
 struct TcArgs {
@@ -66,22 +75,26 @@ struct Smem {
   static constexpr int kKStage = TN * HD * ESZ;
   static constexpr int kVStage = TN * HDV * ESZ;
   static constexpr int kBarOff = kQBytes + KST * kKStage + VST * kVStage;
-  static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1 + 4;
-  static constexpr int kBytes = kBarOff + kNumBars * 8 + 32;   // + abort flags, TMEM base, two work-id slots
+  static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1 + 4 + 2;
+  static constexpr int kItemOff = kBarOff + ((kNumBars * 8 + 16 + 15) & ~15);   // after abort flags and TMEM base
+  static constexpr int kBytes = kItemOff + 2 * 64;             // two mailbox slots of one decoded work item each
 };
 
-// All roles derive the same tile geometry from the same inputs.
-struct Item {
-  int b, h, pair;
-  int q0, seqlen_q, seqlen_k, k0, leftpad;
+// One work item, decoded once by the TMA thread and handed to every role through shared memory (64 bytes).
+struct alignas(16) Item {
+  int b, h, pair, q0;
+  int seqlen_q, seqlen_k, k0, leftpad;
   int lo[2], hi[2];   // key-block range per tile
   int ulo, uhi;       // union
-  bool valid;
+  int valid;
+  int w;              // work id; >= num_items ends the role loops
 };
+static_assert(sizeof(Item) == 64, "mailbox slot");
 
 __device__ __forceinline__ Item decode_item(const TcArgs& a, int w) {
   const KParams& p = a.kp;
   Item it;
+  it.w = w;
   const int per_slot = p.batch * p.hq;
   const int slot = w / per_slot, rem = w - slot * per_slot;
   it.pair = a.max_pairs - 1 - slot;          // heavy (late) tiles first under causal masking
@@ -169,7 +182,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   const uint32_t bar_drain = bar_o_empty + 16;           // MMA warp's private drain barrier
   const uint32_t bar_w_full = bar_drain + 8;             // [2] work id published by the TMA thread
   const uint32_t bar_w_empty = bar_w_full + 16;          // [2] read by the MMA thread and the 8 softmax warps
-  volatile int* s_work = reinterpret_cast<volatile int*>(sm + SM::kBarOff + SM::kNumBars * 8 + 16);
+  const uint32_t bar_p_tail = bar_w_empty + 16;          // [2] the last quarter of P_t is in TMEM
+  Item* s_item = reinterpret_cast<Item*>(sm + SM::kItemOff);   // [2]
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + SM::kBarOff + SM::kNumBars * 8);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sm + SM::kBarOff + SM::kNumBars * 8 + 8);
 
@@ -182,6 +196,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + 8 * t, 1); mbar_init(bar_p_full + 8 * t, 4);     // one elected arrival per softmax warp
       mbar_init(bar_o_full + 8 * t, 1); mbar_init(bar_o_empty + 8 * t, 4);
+      mbar_init(bar_p_tail + 8 * t, 4);
     }
     mbar_init(bar_drain, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(bar_w_full + 8 * i, 1); mbar_init(bar_w_empty + 8 * i, 9); }
@@ -210,24 +225,32 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       uint32_t wcnt = 0;
       // work items are handed out heaviest first through one global counter; every role of this CTA learns the
       // id from a two-slot mailbox in shared memory
-      auto fetch_and_publish = [&]() -> int {
+      auto fetch_and_publish = [&]() -> Item {
+        Item it;
+        it.w = 0x7fffffff;
         const uint32_t slot = wcnt & 1;
         if (!wait_or_abort(bar_w_empty + 8 * slot, ((wcnt >> 1) & 1) ^ 1, s_abort)) {
           report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA);
           ok = false;
-          return 0x7fffffff;
+          return it;
         }
         const int w = atomicAdd(p.counters, 1);
-        s_work[slot] = w;
-        mbar_arrive(bar_w_full + 8 * slot);
+        if (w < a.num_items) it = decode_item(a, w);   // sequence bounds are read from global memory once per item
+        else it.w = w;
+        const int4* src = reinterpret_cast<const int4*>(&it);
+        int4* dst = reinterpret_cast<int4*>(&s_item[slot]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) dst[i] = src[i];
+        mbar_arrive(bar_w_full + 8 * slot);   // release: the slot is visible to whoever observes the phase
         ++wcnt;
-        return w;
+        return it;
       };
-      int w_next = fetch_and_publish();
-      for (int w = w_next; w < a.num_items && ok; w = w_next) {
-        w_next = fetch_and_publish();   // one item ahead: the counter's round trip hides behind this item's loads
-        const Item it = decode_item(a, w);
-        if (!it.valid || it.uhi <= it.ulo) continue;
+      Item it_next = fetch_and_publish();
+      while (it_next.w < a.num_items && ok) {
+        const Item it = it_next;
+        // the next item is fetched one ahead, but only after this item's first loads are on their way: the
+        // counter round trip and the decoding then hide behind them
+        if (!it.valid || it.uhi <= it.ulo) { it_next = fetch_and_publish(); continue; }
         ok = wait_or_abort(bar_q_empty, (qcnt & 1) ^ 1, s_abort);
         if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
         mbar_expect_tx(bar_q_full, SM::kQBytes);
@@ -292,6 +315,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
             }
             vr.advance();
           }
+          if (nb == it.ulo) it_next = fetch_and_publish();
         }
       }
       if (!ok) *s_abort = 1;
@@ -351,11 +375,13 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         umma_commit(bar_s_full + 8 * t);
       }
     };
-    auto issue_pv = [&](int t, uint32_t vslot, bool first) {
+    constexpr int kPvSteps = TN / KEL;                          // MMAs per PV
+    constexpr int kPvHead = kPSplit ? kPvSteps * 3 / 4 : kPvSteps;   // ... that need only the first 96 keys of P
+    auto issue_pv = [&](int t, uint32_t vslot, bool first, int s_lo, int s_hi) {
       const uint64_t vd = vd0 + (uint64_t)(vslot * (SM::kVStage >> 4));
       if (elect_one()) {
 #pragma unroll
-        for (int ks = 0; ks < TN / KEL; ++ks)   // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
+        for (int ks = s_lo; ks < s_hi; ++ks)    // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
           umma_ts<F8>(tmem_u + 256 + t * 128, tmem_u + t * TN + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
                       (!first || ks > 0) ? 1u : 0u);
       }
@@ -366,16 +392,15 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     while (true) {
       const uint32_t slot = wcnt & 1;
       wait(bar_w_full + 8 * slot, (wcnt >> 1) & 1);
-      const int w = __shfl_sync(FULL, s_work[slot], 0);
+      const int4 ra = reinterpret_cast<const int4*>(&s_item[slot])[2], rb = reinterpret_cast<const int4*>(&s_item[slot])[3];
+      // block ranges, broadcast so that every loop bound below is warp-uniform
+      const int lo0 = __shfl_sync(FULL, ra.x, 0), lo1 = __shfl_sync(FULL, ra.y, 0);
+      const int hi0 = __shfl_sync(FULL, ra.z, 0), hi1 = __shfl_sync(FULL, ra.w, 0);
+      const int ulo = __shfl_sync(FULL, rb.x, 0), uhi = __shfl_sync(FULL, rb.y, 0);
+      const int valid = __shfl_sync(FULL, rb.z, 0), w = __shfl_sync(FULL, rb.w, 0);
       if (elect_one()) mbar_arrive(bar_w_empty + 8 * slot);
       ++wcnt;
       if (__any_sync(FULL, fail) || w >= a.num_items) break;
-      const Item it0 = decode_item(a, w);
-      // block ranges, broadcast so that every loop bound below is warp-uniform
-      const int lo0 = __shfl_sync(FULL, it0.lo[0], 0), hi0 = __shfl_sync(FULL, it0.hi[0], 0);
-      const int lo1 = __shfl_sync(FULL, it0.lo[1], 0), hi1 = __shfl_sync(FULL, it0.hi[1], 0);
-      const int ulo = __shfl_sync(FULL, it0.ulo, 0), uhi = __shfl_sync(FULL, it0.uhi, 0);
-      const int valid = __shfl_sync(FULL, (int)it0.valid, 0);
       if (!valid || uhi <= ulo) continue;
       const int lo[2] = {lo0, lo1}, hi[2] = {hi0, hi1};
       wait(bar_q_full, qcnt & 1);
@@ -390,6 +415,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           if (ulo >= lo[t] && ulo < hi[t]) issue_qk(t, ks);
         commit(bar_k_empty + 8 * ks);
         kr.advance();
+        if (ulo + 1 == uhi) commit(bar_q_empty);   // that was the item's only QK: Q may be replaced once it has run
       }
       for (int i = ulo; i < uhi; ++i) {
         const bool nxt = i + 1 < uhi;
@@ -406,9 +432,15 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
               ++oecnt[t];
             }
             wait(bar_p_full + 8 * t, pcnt[t] & 1);
-            ++pcnt[t];
             tc_fence_after_sync();
-            issue_pv(t, vs, first);
+            issue_pv(t, vs, first, 0, kPvHead);
+            if constexpr (kPSplit) {
+              // the softmax is still working on the last 32 keys while the tensor pipe runs the first 96
+              wait(bar_p_tail + 8 * t, pcnt[t] & 1);
+              tc_fence_after_sync();
+              issue_pv(t, vs, first, kPvHead, kPvSteps);
+            }
+            ++pcnt[t];
             if (i + 1 == hi[t]) commit(bar_o_full + 8 * t);
           }
           if (nxt && i + 1 >= lo[t] && i + 1 < hi[t]) {
@@ -420,6 +452,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
             issue_qk(t, ks);
           }
         }
+        // the item's last QK has been issued: the next item's Q tiles load during this item's last block
+        if (i + 2 == uhi) commit(bar_q_empty);
         commit(bar_v_empty + 8 * vs);
         vr.advance();
         if (nxt) {
@@ -428,7 +462,6 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           kr.advance();
         }
       }
-      commit(bar_q_empty);
     }
     // drain: all MMAs this warp issued must have retired before TMEM is released
     commit(bar_drain);
@@ -447,17 +480,21 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     bool ok = true;
 
     uint32_t wcnt = 0;
-    auto next_work = [&]() -> int {
+    auto next_work = [&]() -> Item {
+      Item it;
+      it.w = 0x7fffffff;
       const uint32_t slot = wcnt & 1;
-      if (!wait_or_abort(bar_w_full + 8 * slot, (wcnt >> 1) & 1, s_abort)) { ok = false; return 0x7fffffff; }
-      const int w = s_work[slot];
+      if (!wait_or_abort(bar_w_full + 8 * slot, (wcnt >> 1) & 1, s_abort)) { ok = false; return it; }
+      const int4* src = reinterpret_cast<const int4*>(&s_item[slot]);
+      int4* dst = reinterpret_cast<int4*>(&it);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dst[i] = src[i];
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_w_empty + 8 * slot);
       ++wcnt;
-      return w;
+      return it;
     };
-    for (int w = next_work(); w < a.num_items && ok; w = next_work()) {
-      const Item it = decode_item(a, w);
+    for (Item it = next_work(); it.w < a.num_items && ok; it = next_work()) {
       if (!it.valid) continue;
       const int row0 = it.pair * 2 * TM + t * TM;
       if (row0 >= it.seqlen_q) continue;           // this tile owns no row
@@ -523,7 +560,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
-            for (int j = 0; j < 32; ++j) mxa[j & 7] = fmaxf(mxa[j & 7], __uint_as_float(sreg[c][j]));
+            for (int j = 0; j < 32; j += 2)
+              mxa[(j >> 1) & 7] = fmax3(mxa[(j >> 1) & 7], __uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1]));
           mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
                      fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
         }
@@ -540,49 +578,9 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           rescale = true;
         }
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-        float2 psum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-        const float2 c2 = make_float2(c_mul, c_mul), nm2 = make_float2(neg_m, neg_m);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          if constexpr (!F8) {
-            uint32_t pk[16];
-#pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const float2 y = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
-              const float2 pp = make_float2(ex2(y.x), ex2(y.y));
-              psum[(j >> 1) & 3] = fadd2(psum[(j >> 1) & 3], pp);
-              pk[j >> 1] = pack2<TO>(pp.x, pp.y);
-            }
-            tmem_st16(tS + c * 16, pk);
-          } else {
-            // four e4m3 probabilities per TMEM column.  The row sum is taken over the ROUNDED probabilities, so
-            // that numerator (P V on the tensor cores) and denominator describe the same weights.
-            uint32_t pk[8];
-            __half2 hs[4] = {__half2(), __half2(), __half2(), __half2()};
-#pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              const float2 y0 = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
-              const float2 y1 = ffma2(make_float2(__uint_as_float(sreg[c][j + 2]), __uint_as_float(sreg[c][j + 3])), c2, nm2);
-              const float2 p0 = make_float2(ex2(y0.x), ex2(y0.y)), p1 = make_float2(ex2(y1.x), ex2(y1.y));
-              psum[(j >> 2) & 3] = fadd2(psum[(j >> 2) & 3], fadd2(p0, p1));
-              const uint32_t q4 = pack4_e4m3(p0.x, p0.y, p1.x, p1.y);
-              pk[j >> 2] = q4;
-              const uint32_t h0 = e4m3x2_to_f16x2((uint16_t)(q4 & 0xffffu)), h1 = e4m3x2_to_f16x2((uint16_t)(q4 >> 16));
-              hs[(j >> 2) & 3] = __hadd2(hs[(j >> 2) & 3],
-                                         __hadd2(*reinterpret_cast<const __half2*>(&h0), *reinterpret_cast<const __half2*>(&h1)));
-            }
-            tmem_st8(tS + c * 8, pk);
-            const float2 f01 = __half22float2(__hadd2(hs[0], hs[1])), f23 = __half22float2(__hadd2(hs[2], hs[3]));
-            lr += (f01.x + f23.x) + (f01.y + f23.y);
-          }
-        }
-        {
-          const float2 s01 = fadd2(psum[0], psum[1]), s23 = fadd2(psum[2], psum[3]);
-          const float2 s4 = fadd2(s01, s23);
-          l += s4.x + s4.y;
-        }
         if (__any_sync(0xffffffffu, rescale)) {
-          // O_t of the previous blocks is complete: the commit behind s_full also covered PV_t(i-1)
+          // O_t of the previous blocks is complete: the commit behind s_full also covered PV_t(i-1); PV_t(i)
+          // cannot start before this thread's arrival below
 #pragma unroll 1
           for (int c = 0; c < HDV / 32; ++c) {
             uint32_t o[32];
@@ -593,10 +591,69 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
             tmem_st32(tO + c * 32, o);
           }
         }
+        float2 psum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+        const float2 c2 = make_float2(c_mul, c_mul), nm2 = make_float2(neg_m, neg_m);
+        // EMU of every 4 column pairs compute 2^x with a cubic on the FMA pipe; the special-function unit
+        // (16 results per cycle and SM) is as loaded as the tensor pipe in this kernel
+        auto exp_and_store = [&](auto emu_tag) {
+          constexpr int EMU = decltype(emu_tag)::value;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if constexpr (!F8) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                const float2 y = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
+                float2 pp;
+                if (((j >> 1) & 3) < EMU) pp = ex2_poly2(y);
+                else pp = make_float2(ex2(y.x), ex2(y.y));
+                psum[(j >> 1) & 3] = fadd2(psum[(j >> 1) & 3], pp);
+                pk[j >> 1] = pack2<TO>(pp.x, pp.y);
+              }
+              tmem_st16(tS + c * 16, pk);
+            } else {
+              // four e4m3 probabilities per TMEM column.  The row sum is taken over the ROUNDED probabilities, so
+              // that numerator (P V on the tensor cores) and denominator describe the same weights.
+              uint32_t pk[8];
+              __half2 hs[4] = {__half2(), __half2(), __half2(), __half2()};
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const float2 y0 = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
+                const float2 y1 = ffma2(make_float2(__uint_as_float(sreg[c][j + 2]), __uint_as_float(sreg[c][j + 3])), c2, nm2);
+                float2 p0, p1;
+                if (((j >> 2) & 3) < EMU) { p0 = ex2_poly2(y0); p1 = ex2_poly2(y1); }
+                else { p0 = make_float2(ex2(y0.x), ex2(y0.y)); p1 = make_float2(ex2(y1.x), ex2(y1.y)); }
+                psum[(j >> 2) & 3] = fadd2(psum[(j >> 2) & 3], fadd2(p0, p1));
+                const uint32_t q4 = pack4_e4m3(p0.x, p0.y, p1.x, p1.y);
+                pk[j >> 2] = q4;
+                const uint32_t h0 = e4m3x2_to_f16x2((uint16_t)(q4 & 0xffffu)), h1 = e4m3x2_to_f16x2((uint16_t)(q4 >> 16));
+                hs[(j >> 2) & 3] = __hadd2(hs[(j >> 2) & 3],
+                                           __hadd2(*reinterpret_cast<const __half2*>(&h0), *reinterpret_cast<const __half2*>(&h1)));
+              }
+              tmem_st8(tS + c * 8, pk);
+              const float2 f01 = __half22float2(__hadd2(hs[0], hs[1])), f23 = __half22float2(__hadd2(hs[2], hs[3]));
+              lr += (f01.x + f23.x) + (f01.y + f23.y);
+            }
+            if (kPSplit && c == 2) {   // the first 96 keys of P are enough for three quarters of PV_t
+              tmem_wait_st();
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar_p_full + 8 * t);
+            }
+          }
+        };
+        // the cubic never returns exactly 0, so it is used only on blocks without masked columns
+        if (kEmuPairs > 0 && full) exp_and_store(std::integral_constant<int, kEmuPairs>{});
+        else exp_and_store(std::integral_constant<int, 0>{});
+        {
+          const float2 s01 = fadd2(psum[0], psum[1]), s23 = fadd2(psum[2], psum[3]);
+          const float2 s4 = fadd2(s01, s23);
+          l += s4.x + s4.y;
+        }
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_p_full + 8 * t);
+        if (lane == 0) mbar_arrive((kPSplit ? bar_p_tail : bar_p_full) + 8 * t);
       }
       if (!ok) break;
 
