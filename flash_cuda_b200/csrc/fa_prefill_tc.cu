@@ -37,15 +37,6 @@ constexpr int WARP_MMA = 8, WARP_TMA = 9;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
-// experiment knobs
-#ifndef FA_TC_EMU
-#define FA_TC_EMU 0        // of every 4 column pairs, how many take 2^x on the FMA pipe instead of the SFU
-#endif
-#ifndef FA_TC_PSPLIT
-#define FA_TC_PSPLIT 0     // P is handed to the MMA thread in two parts: the first 96 keys, then the last 32
-#endif
-constexpr int kEmuPairs = FA_TC_EMU;
-constexpr bool kPSplit = FA_TC_PSPLIT != 0;
 enum Role : unsigned { ROLE_TMA = 1, ROLE_MMA = 2, ROLE_SOFTMAX = 3, ROLE_EPILOGUE = 4 };
 
 struct TcArgs {
@@ -75,7 +66,7 @@ struct Smem {
   static constexpr int kKStage = TN * HD * ESZ;
   static constexpr int kVStage = TN * HDV * ESZ;
   static constexpr int kBarOff = kQBytes + KST * kKStage + VST * kVStage;
-  static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1 + 4 + 2;
+  static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1 + 4;
   static constexpr int kItemOff = kBarOff + ((kNumBars * 8 + 16 + 15) & ~15);   // after abort flags and TMEM base
   static constexpr int kBytes = kItemOff + 2 * 64;             // two mailbox slots of one decoded work item each
 };
@@ -182,7 +173,6 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   const uint32_t bar_drain = bar_o_empty + 16;           // MMA warp's private drain barrier
   const uint32_t bar_w_full = bar_drain + 8;             // [2] work id published by the TMA thread
   const uint32_t bar_w_empty = bar_w_full + 16;          // [2] read by the MMA thread and the 8 softmax warps
-  const uint32_t bar_p_tail = bar_w_empty + 16;          // [2] the last quarter of P_t is in TMEM
   Item* s_item = reinterpret_cast<Item*>(sm + SM::kItemOff);   // [2]
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + SM::kBarOff + SM::kNumBars * 8);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sm + SM::kBarOff + SM::kNumBars * 8 + 8);
@@ -196,7 +186,6 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + 8 * t, 1); mbar_init(bar_p_full + 8 * t, 4);     // one elected arrival per softmax warp
       mbar_init(bar_o_full + 8 * t, 1); mbar_init(bar_o_empty + 8 * t, 4);
-      mbar_init(bar_p_tail + 8 * t, 4);
     }
     mbar_init(bar_drain, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(bar_w_full + 8 * i, 1); mbar_init(bar_w_empty + 8 * i, 9); }
@@ -375,13 +364,11 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         umma_commit(bar_s_full + 8 * t);
       }
     };
-    constexpr int kPvSteps = TN / KEL;                          // MMAs per PV
-    constexpr int kPvHead = kPSplit ? kPvSteps * 3 / 4 : kPvSteps;   // ... that need only the first 96 keys of P
-    auto issue_pv = [&](int t, uint32_t vslot, bool first, int s_lo, int s_hi) {
+    auto issue_pv = [&](int t, uint32_t vslot, bool first) {
       const uint64_t vd = vd0 + (uint64_t)(vslot * (SM::kVStage >> 4));
       if (elect_one()) {
 #pragma unroll
-        for (int ks = s_lo; ks < s_hi; ++ks)    // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
+        for (int ks = 0; ks < TN / KEL; ++ks)   // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
           umma_ts<F8>(tmem_u + 256 + t * 128, tmem_u + t * TN + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
                       (!first || ks > 0) ? 1u : 0u);
       }
@@ -433,13 +420,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
             }
             wait(bar_p_full + 8 * t, pcnt[t] & 1);
             tc_fence_after_sync();
-            issue_pv(t, vs, first, 0, kPvHead);
-            if constexpr (kPSplit) {
-              // the softmax is still working on the last 32 keys while the tensor pipe runs the first 96
-              wait(bar_p_tail + 8 * t, pcnt[t] & 1);
-              tc_fence_after_sync();
-              issue_pv(t, vs, first, kPvHead, kPvSteps);
-            }
+            issue_pv(t, vs, first);
             ++pcnt[t];
             if (i + 1 == hi[t]) commit(bar_o_full + 8 * t);
           }
@@ -593,10 +574,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         }
         float2 psum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
         const float2 c2 = make_float2(c_mul, c_mul), nm2 = make_float2(neg_m, neg_m);
-        // EMU of every 4 column pairs compute 2^x with a cubic on the FMA pipe; the special-function unit
-        // (16 results per cycle and SM) is as loaded as the tensor pipe in this kernel
-        auto exp_and_store = [&](auto emu_tag) {
-          constexpr int EMU = decltype(emu_tag)::value;
+        {
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             if constexpr (!F8) {
@@ -604,9 +582,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
               for (int j = 0; j < 32; j += 2) {
                 const float2 y = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
-                float2 pp;
-                if (((j >> 1) & 3) < EMU) pp = ex2_poly2(y);
-                else pp = make_float2(ex2(y.x), ex2(y.y));
+                const float2 pp = make_float2(ex2(y.x), ex2(y.y));
                 psum[(j >> 1) & 3] = fadd2(psum[(j >> 1) & 3], pp);
                 pk[j >> 1] = pack2<TO>(pp.x, pp.y);
               }
@@ -620,9 +596,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
               for (int j = 0; j < 32; j += 4) {
                 const float2 y0 = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
                 const float2 y1 = ffma2(make_float2(__uint_as_float(sreg[c][j + 2]), __uint_as_float(sreg[c][j + 3])), c2, nm2);
-                float2 p0, p1;
-                if (((j >> 2) & 3) < EMU) { p0 = ex2_poly2(y0); p1 = ex2_poly2(y1); }
-                else { p0 = make_float2(ex2(y0.x), ex2(y0.y)); p1 = make_float2(ex2(y1.x), ex2(y1.y)); }
+                const float2 p0 = make_float2(ex2(y0.x), ex2(y0.y)), p1 = make_float2(ex2(y1.x), ex2(y1.y));
                 psum[(j >> 2) & 3] = fadd2(psum[(j >> 2) & 3], fadd2(p0, p1));
                 const uint32_t q4 = pack4_e4m3(p0.x, p0.y, p1.x, p1.y);
                 pk[j >> 2] = q4;
@@ -634,17 +608,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
               const float2 f01 = __half22float2(__hadd2(hs[0], hs[1])), f23 = __half22float2(__hadd2(hs[2], hs[3]));
               lr += (f01.x + f23.x) + (f01.y + f23.y);
             }
-            if (kPSplit && c == 2) {   // the first 96 keys of P are enough for three quarters of PV_t
-              tmem_wait_st();
-              tc_fence_before_sync();
-              __syncwarp();
-              if (lane == 0) mbar_arrive(bar_p_full + 8 * t);
-            }
           }
-        };
-        // the cubic never returns exactly 0, so it is used only on blocks without masked columns
-        if (kEmuPairs > 0 && full) exp_and_store(std::integral_constant<int, kEmuPairs>{});
-        else exp_and_store(std::integral_constant<int, 0>{});
+        }
         {
           const float2 s01 = fadd2(psum[0], psum[1]), s23 = fadd2(psum[2], psum[3]);
           const float2 s4 = fadd2(s01, s23);
@@ -653,7 +618,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive((kPSplit ? bar_p_tail : bar_p_full) + 8 * t);
+        if (lane == 0) mbar_arrive(bar_p_full + 8 * t);
       }
       if (!ok) break;
 

@@ -309,32 +309,6 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
   return r;
 }
-// 2^x for a pair on the FMA and integer pipes instead of the special-function unit.  x is split into
-// floor(x) (taken from the low mantissa bits of x + 1.5*2^23 rounded toward -inf) and a fraction in [0,1);
-// 2^fraction is a cubic (minimax with p(0) = 1, relative error 8.6e-5, below 16-bit rounding of the result)
-// and floor(x) is added into the exponent field.  Inputs below -127 are clamped: the result is then a
-// denormal of about 6e-39 rather than exactly 0, so callers use it only where every input is finite and some
-// input of the row is near the maximum.
-__device__ __forceinline__ float2 ex2_poly2(float2 x) {
-  constexpr float kMagic = 12582912.f;   // 1.5 * 2^23
-  x.x = fmaxf(x.x, -127.f);
-  x.y = fmaxf(x.y, -127.f);
-  unsigned long long rx, rm, rr;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(rx) : "f"(x.x), "f"(x.y));
-  asm("mov.b64 %0, {%1, %1};" : "=l"(rm) : "f"(kMagic));
-  asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(rr) : "l"(rx), "l"(rm));
-  float2 r;
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(rr));
-  const float2 fl = fadd2(r, make_float2(-kMagic, -kMagic));                 // floor(x), exact
-  const float2 f = ffma2(fl, make_float2(-1.f, -1.f), x);                     // x - floor(x)
-  float2 p = ffma2(f, make_float2(0.07706724f, 0.07706724f), make_float2(0.22764498f, 0.22764498f));
-  p = ffma2(p, f, make_float2(0.69511664f, 0.69511664f));
-  p = ffma2(p, f, make_float2(1.f, 1.f));
-  float2 o;
-  o.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(r.x) << 23));
-  o.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(r.y) << 23));
-  return o;
-}
 // two fp32 -> packed 16-bit pair, `lo` in bits [0,16)
 template <typename T>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi);
