@@ -66,7 +66,7 @@ struct Smem {
   static constexpr int kKStage = TN * HD * ESZ;
   static constexpr int kVStage = TN * HDV * ESZ;
   static constexpr int kBarOff = kQBytes + KST * kKStage + VST * kVStage;
-  static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1 + 4;
+  static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1 + 4 + 1;
   static constexpr int kItemOff = kBarOff + ((kNumBars * 8 + 16 + 15) & ~15);   // after abort flags and TMEM base
   static constexpr int kBytes = kItemOff + 2 * 64;             // two mailbox slots of one decoded work item each
 };
@@ -173,6 +173,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   const uint32_t bar_drain = bar_o_empty + 16;           // MMA warp's private drain barrier
   const uint32_t bar_w_full = bar_drain + 8;             // [2] work id published by the TMA thread
   const uint32_t bar_w_empty = bar_w_full + 16;          // [2] read by the MMA thread and the 8 softmax warps
+  const uint32_t bar_k0_full = bar_w_empty + 16;         // K of an item's first block (later K tiles ride on v_full)
   Item* s_item = reinterpret_cast<Item*>(sm + SM::kItemOff);   // [2]
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + SM::kBarOff + SM::kNumBars * 8);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sm + SM::kBarOff + SM::kNumBars * 8 + 8);
@@ -188,6 +189,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       mbar_init(bar_o_full + 8 * t, 1); mbar_init(bar_o_empty + 8 * t, 4);
     }
     mbar_init(bar_drain, 1);
+    mbar_init(bar_k0_full, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(bar_w_full + 8 * i, 1); mbar_init(bar_w_empty + 8 * i, 9); }
     s_abort[0] = 0;
     s_abort[1] = 0;   // [1] is never raised: waits that may only end by completion or time limit
@@ -207,7 +209,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   if (warp == WARP_TMA) {
     // =========================================== TMA producer ===========================================
     if (lane == 0) {
-      uint32_t qcnt = 0;
+      uint32_t qcnt = 0, k0cnt = 0;
       Ring<KST> kr;
       Ring<VST> vr;
       bool ok = true;
@@ -251,58 +253,47 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
                         it.q0 + it.pair * 2 * TM + t * TM, bar_q_full);
         ++qcnt;
         const int hk = it.h / p.rep;
-        for (int nb = it.ulo; nb < it.uhi; ++nb) {
-          // K tile
-          {
-            const uint32_t s = kr.slot;
-            ok = wait_or_abort(bar_k_empty + 8 * s, kr.phase ^ 1u, s_abort);
-            if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
-            mbar_expect_tx(bar_k_full + 8 * s, SM::kKStage);
-            const uint32_t dst = sK + s * SM::kKStage;
-            if (p.page_table == nullptr) {
-#pragma unroll
-              for (int cb = 0; cb < HD / EPB; ++cb)
-                tma_load_2d(dst + cb * (TN * 128), &map_k, hk * HD + cb * EPB, it.k0 + nb * TN, bar_k_full + 8 * s);
-            } else {
-              for (int r = 0; r < TN; r += a.kv_box_rows) {
-                const int kk = nb * TN + r;
-                int y = a.kv_total_rows;   // beyond the sequence: out of range => zeros
-                if (kk < it.seqlen_k) {
-                  const int lp = p.page_shift >= 0 ? (kk >> p.page_shift) : (kk / p.page_size);
-                  y = p.page_table[(int64_t)it.b * p.page_table_stride + lp] * p.page_size + (kk - lp * p.page_size);
-                }
-#pragma unroll
-                for (int cb = 0; cb < HD / EPB; ++cb)
-                  tma_load_2d(dst + cb * (TN * 128) + r * 128, &map_k, hk * HD + cb * EPB, y, bar_k_full + 8 * s);
+        // one K or V tile of key block nb into `dst`, completing on `bar`
+        auto load_tile = [&](const CUtensorMap* map, int width, uint32_t dst, int nb, uint32_t bar) {
+          if (p.page_table == nullptr) {
+            for (int cb = 0; cb < width / EPB; ++cb)
+              tma_load_2d(dst + cb * (TN * 128), map, hk * width + cb * EPB, it.k0 + nb * TN, bar);
+          } else {
+            for (int r = 0; r < TN; r += a.kv_box_rows) {
+              const int kk = nb * TN + r;
+              int y = a.kv_total_rows;   // beyond the sequence: out of range => zeros
+              if (kk < it.seqlen_k) {
+                const int lp = p.page_shift >= 0 ? (kk >> p.page_shift) : (kk / p.page_size);
+                y = p.page_table[(int64_t)it.b * p.page_table_stride + lp] * p.page_size + (kk - lp * p.page_size);
               }
+              for (int cb = 0; cb < width / EPB; ++cb)
+                tma_load_2d(dst + cb * (TN * 128) + r * 128, map, hk * width + cb * EPB, y, bar);
             }
-            kr.advance();
           }
-          // V tile
-          {
-            const uint32_t s = vr.slot;
-            ok = wait_or_abort(bar_v_empty + 8 * s, vr.phase ^ 1u, s_abort);
-            if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
-            mbar_expect_tx(bar_v_full + 8 * s, SM::kVStage);
-            const uint32_t dst = sV + s * SM::kVStage;
-            if (p.page_table == nullptr) {
-#pragma unroll
-              for (int cb = 0; cb < HDV / EPB; ++cb)
-                tma_load_2d(dst + cb * (TN * 128), &map_v, hk * HDV + cb * EPB, it.k0 + nb * TN, bar_v_full + 8 * s);
-            } else {
-              for (int r = 0; r < TN; r += a.kv_box_rows) {
-                const int kk = nb * TN + r;
-                int y = a.kv_total_rows;
-                if (kk < it.seqlen_k) {
-                  const int lp = p.page_shift >= 0 ? (kk >> p.page_shift) : (kk / p.page_size);
-                  y = p.page_table[(int64_t)it.b * p.page_table_stride + lp] * p.page_size + (kk - lp * p.page_size);
-                }
-#pragma unroll
-                for (int cb = 0; cb < HDV / EPB; ++cb)
-                  tma_load_2d(dst + cb * (TN * 128) + r * 128, &map_v, hk * HDV + cb * EPB, y, bar_v_full + 8 * s);
-              }
-            }
-            vr.advance();
+        };
+        // K of the first block has a barrier of its own; every later K tile arrives together with the V tile of
+        // the block before it (the MMA warp needs both at the same point), so the consumer waits once per block
+        {
+          const uint32_t s = kr.slot;
+          ok = wait_or_abort(bar_k_empty + 8 * s, kr.phase ^ 1u, s_abort);
+          if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+          mbar_expect_tx(bar_k0_full, SM::kKStage);
+          load_tile(&map_k, HD, sK + s * SM::kKStage, it.ulo, bar_k0_full);
+          kr.advance();
+          ++k0cnt;
+        }
+        for (int nb = it.ulo; nb < it.uhi; ++nb) {
+          const bool nxt = nb + 1 < it.uhi;
+          const uint32_t vs = vr.slot, ks = kr.slot;
+          ok = wait_or_abort(bar_v_empty + 8 * vs, vr.phase ^ 1u, s_abort);
+          if (ok && nxt) ok = wait_or_abort(bar_k_empty + 8 * ks, kr.phase ^ 1u, s_abort);
+          if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+          mbar_expect_tx(bar_v_full + 8 * vs, SM::kVStage + (nxt ? SM::kKStage : 0));
+          load_tile(&map_v, HDV, sV + vs * SM::kVStage, nb, bar_v_full + 8 * vs);
+          vr.advance();
+          if (nxt) {
+            load_tile(&map_k, HD, sK + ks * SM::kKStage, nb + 1, bar_v_full + 8 * vs);
+            kr.advance();
           }
           if (nb == it.ulo) it_next = fetch_and_publish();
         }
@@ -310,9 +301,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       if (!ok) *s_abort = 1;
       // drain: every copy this thread issued must have landed before the CTA may leave
       if (qcnt > 0) wait_or_abort(bar_q_full, (qcnt - 1) & 1, s_abort + 1 /* never set: pure time limit */);
-      for (uint32_t s = 0; s < (uint32_t)KST; ++s) {
-        if (kr.n > s) { const uint32_t last = (kr.n - 1 - s) / KST; wait_or_abort(bar_k_full + 8 * s, last & 1, s_abort + 1); }
-      }
+      if (k0cnt > 0) wait_or_abort(bar_k0_full, (k0cnt - 1) & 1, s_abort + 1);
       for (uint32_t s = 0; s < (uint32_t)VST; ++s) {
         if (vr.n > s) { const uint32_t last = (vr.n - 1 - s) / VST; wait_or_abort(bar_v_full + 8 * s, last & 1, s_abort + 1); }
       }
@@ -334,7 +323,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     constexpr uint32_t idesc_pv = umma_idesc(kFmt, TM, HDV, true);
     constexpr uint32_t FULL = 0xffffffffu;
     const uint32_t tmem_u = __shfl_sync(FULL, tmem, 0);
-    uint32_t qcnt = 0, pcnt[2] = {0, 0}, oecnt[2] = {0, 0};
+    const bool leader = elect_one();   // the same lane every time; decided once
+    uint32_t qcnt = 0, k0cnt = 0, pcnt[2] = {0, 0}, oecnt[2] = {0, 0};
     Ring<KST> kr;
     Ring<VST> vr;
     // A wait that runs out does not branch out of the loops (that would make every loop-carried value
@@ -354,7 +344,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     auto issue_qk = [&](int t, uint32_t kslot) {
       const uint64_t qd = qd0 + (uint64_t)(t * ((TM * HD * ESZ) >> 4));
       const uint64_t kd = kd0 + (uint64_t)(kslot * (SM::kKStage >> 4));
-      if (elect_one()) {
+      if (leader) {
 #pragma unroll
         for (int ks = 0; ks < HD / KEL; ++ks) {
           constexpr int kBlk = (TM * 128) >> 4;
@@ -366,14 +356,14 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     };
     auto issue_pv = [&](int t, uint32_t vslot, bool first) {
       const uint64_t vd = vd0 + (uint64_t)(vslot * (SM::kVStage >> 4));
-      if (elect_one()) {
+      if (leader) {
 #pragma unroll
         for (int ks = 0; ks < TN / KEL; ++ks)   // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
           umma_ts<F8>(tmem_u + 256 + t * 128, tmem_u + t * TN + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
                       (!first || ks > 0) ? 1u : 0u);
       }
     };
-    auto commit = [&](uint32_t bar) { if (elect_one()) umma_commit(bar); };
+    auto commit = [&](uint32_t bar) { if (leader) umma_commit(bar); };
 
     uint32_t wcnt = 0;
     while (true) {
@@ -385,7 +375,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       const int hi0 = __shfl_sync(FULL, ra.z, 0), hi1 = __shfl_sync(FULL, ra.w, 0);
       const int ulo = __shfl_sync(FULL, rb.x, 0), uhi = __shfl_sync(FULL, rb.y, 0);
       const int valid = __shfl_sync(FULL, rb.z, 0), w = __shfl_sync(FULL, rb.w, 0);
-      if (elect_one()) mbar_arrive(bar_w_empty + 8 * slot);
+      if (leader) mbar_arrive(bar_w_empty + 8 * slot);
       ++wcnt;
       if (__any_sync(FULL, fail) || w >= a.num_items) break;
       if (!valid || uhi <= ulo) continue;
@@ -395,8 +385,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       // prologue: QK of the first block
       {
         const uint32_t ks = kr.slot;
-        wait(bar_k_full + 8 * ks, kr.phase);
-        tc_fence_after_sync();
+        wait(bar_k0_full, k0cnt & 1);
+        ++k0cnt;
 #pragma unroll
         for (int t = 0; t < 2; ++t)
           if (ulo >= lo[t] && ulo < hi[t]) issue_qk(t, ks);
@@ -408,8 +398,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         const bool nxt = i + 1 < uhi;
         const uint32_t vs = vr.slot;
         const uint32_t ks = kr.slot;          // slot of block i+1 (if any)
-        wait(bar_v_full + 8 * vs, vr.phase);
-        bool k_ready = false;
+        wait(bar_v_full + 8 * vs, vr.phase);   // V of this block and K of the next one
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (i >= lo[t] && i < hi[t]) {
@@ -424,28 +413,20 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
             ++pcnt[t];
             if (i + 1 == hi[t]) commit(bar_o_full + 8 * t);
           }
-          if (nxt && i + 1 >= lo[t] && i + 1 < hi[t]) {
-            if (!k_ready) {
-              wait(bar_k_full + 8 * ks, kr.phase);
-              tc_fence_after_sync();
-              k_ready = true;
-            }
-            issue_qk(t, ks);
-          }
+          if (nxt && i + 1 >= lo[t] && i + 1 < hi[t]) issue_qk(t, ks);
         }
         // the item's last QK has been issued: the next item's Q tiles load during this item's last block
         if (i + 2 == uhi) commit(bar_q_empty);
         commit(bar_v_empty + 8 * vs);
         vr.advance();
         if (nxt) {
-          if (!k_ready) wait(bar_k_full + 8 * ks, kr.phase);   // block i+1 belongs to neither tile: still consume its K slot
           commit(bar_k_empty + 8 * ks);
           kr.advance();
         }
       }
     }
     // drain: all MMAs this warp issued must have retired before TMEM is released
-    commit(bar_drain);
+    if (leader) umma_commit(bar_drain);
     wait_or_abort(bar_drain, 0, s_abort + 1);
   }
   } else {
