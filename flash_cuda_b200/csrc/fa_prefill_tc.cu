@@ -4,11 +4,14 @@
 // both tiles share every K/V tile that TMA brings in.  Warp roles (384 threads):
 //   warps 0-3  softmax of tile 0   (one query row per thread: S row TMEM -> registers -> P row TMEM)
 //   warps 4-7  softmax of tile 1
-//   warp  8    MMA issuer: S_t = Q_t K^T (operands in shared memory), O_t += P_t V (P in TMEM)
-//   warp  9    TMA producer: Q pair, K ring, V ring (no cluster multicast: each CTA loads its own tiles)
+//   warp  8    MMA issuer: S_t = Q_t K^T (operands in shared memory), O_t += P_t V (P in TMEM); the whole
+//              warp runs the control flow (warp-uniform values, uniform registers), one elected lane issues
+//   warp  9    TMA producer (one lane): Q pair, K ring, V ring (no cluster multicast: each CTA loads its own
+//              tiles); also takes work ids from the global counter and decodes them
 //   warps 10-11 idle (they complete the third warpgroup so that register tiers can be set per warpgroup)
 // Work items (256 query rows of one (batch, head); late = heavy tiles first) are handed out through one global
-// atomic counter and a two-slot mailbox in shared memory, so SMs that finish early take more.
+// atomic counter, so SMs that finish early take more; the TMA lane decodes each item once (sequence bounds,
+// key-block ranges) and publishes it, one item ahead, in a two-slot mailbox in shared memory.
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t overlays the first 64
 // columns of S_t once the owning thread has read its S row.
 // The tensor pipe runs [PV0(i), QK0(i+1), PV1(i), QK1(i+1)] so that one tile's softmax overlaps the other
@@ -66,7 +69,7 @@ struct Smem {
   static constexpr int kKStage = TN * HD * ESZ;
   static constexpr int kVStage = TN * HDV * ESZ;
   static constexpr int kBarOff = kQBytes + KST * kKStage + VST * kVStage;
-  static constexpr int kNumBars = 2 + 2 * KST + 2 * VST + 8 + 1 + 4 + 1;
+  static constexpr int kNumBars = 2 + KST + 2 * VST + 8 + 1 + 4 + 1;
   static constexpr int kItemOff = kBarOff + ((kNumBars * 8 + 16 + 15) & ~15);   // after abort flags and TMEM base
   static constexpr int kBytes = kItemOff + 2 * 64;             // two mailbox slots of one decoded work item each
 };
@@ -164,7 +167,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   const uint32_t bars = base + SM::kBarOff;
   // barrier map
   const uint32_t bar_q_full = bars, bar_q_empty = bars + 8;
-  const uint32_t bar_k_full = bars + 16, bar_k_empty = bar_k_full + 8 * KST;
+  const uint32_t bar_k_empty = bars + 16;                // [KST] (K tiles complete on k0_full / v_full, see the TMA role)
   const uint32_t bar_v_full = bar_k_empty + 8 * KST, bar_v_empty = bar_v_full + 8 * VST;
   const uint32_t bar_s_full = bar_v_empty + 8 * VST;     // [2]
   const uint32_t bar_p_full = bar_s_full + 16;           // [2]
@@ -182,7 +185,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
 
   if (tid == 0) {
     mbar_init(bar_q_full, 1); mbar_init(bar_q_empty, 1);
-    for (int s = 0; s < KST; ++s) { mbar_init(bar_k_full + 8 * s, 1); mbar_init(bar_k_empty + 8 * s, 1); }
+    for (int s = 0; s < KST; ++s) mbar_init(bar_k_empty + 8 * s, 1);
     for (int s = 0; s < VST; ++s) { mbar_init(bar_v_full + 8 * s, 1); mbar_init(bar_v_empty + 8 * s, 1); }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + 8 * t, 1); mbar_init(bar_p_full + 8 * t, 4);     // one elected arrival per softmax warp
