@@ -29,6 +29,10 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
+# DRAM traffic per launch measured once with ncu (dram__bytes_read.sum + dram__bytes_write.sum); the captures and
+# their commands are summarised under profiles/.  Prefill was captured at B=2 (133.2 MB) and grows in proportion to B.
+NCU_PREFILL_TRAFFIC_PER_BATCH = 66.6e6
+NCU_DECODE_TRAFFIC = {"bf16": 8.59e9, "fp8": 4.299e9}
 METRIC = "prefill TFLOP/s per job (causal GQA bf16 B=4 Hq=32 Hkv=8 S=4096 d=128); decode HBM GB/s in `decode`"
 L2_BYTES = 126 * 1024 * 1024
 
@@ -263,7 +267,9 @@ def run_ours(args) -> None:
                 "value": gbs * world, "unit": "GB/s", "ms_per_step": dms, "kv_bytes_per_step": kvb,
                 "num_splits": nspl,
                 "roofline": {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                             "frac": gbs / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"]},
+                             "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_DECODE_TRAFFIC[kv_dtype],
+                             "traffic_source": "ncu dram__bytes_read+write per launch of this configuration (profiles/)",
+                             "peak_source": peaks["source"]},
                 "l2": f"KV pool ({kvb / 1e9:.2f} GB) larger than L2",
             }
         except Exception as e:  # reported, never hidden
@@ -287,8 +293,9 @@ def run_ours(args) -> None:
                    "l2": f"{R} rotating input sets of {in_bytes / 1e6:.0f} MB each (> L2 {L2_BYTES / 1e6:.0f} MB)",
                    "flops_per_step_per_gpu": flops},
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                     "frac": per_gpu / peaks["bf16_tflops"], "traffic": None, "peak_source": peaks["source"],
-                     "kernel": "fwd_prefill_tc_kernel", "launch_ms": ms},
+                     "frac": per_gpu / peaks["bf16_tflops"], "traffic": NCU_PREFILL_TRAFFIC_PER_BATCH * args.batch,
+                     "traffic_source": "ncu dram__bytes_read+write of a B=2 launch, scaled by B (profiles/)",
+                     "peak_source": peaks["source"], "kernel": "fwd_prefill_tc_kernel", "launch_ms": ms},
         "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks, "decode": decode, "decode_fp8": decode_fp8, "cpu_baseline": cpu,
         "kernels_per_step": {"prefill": ["fwd_prefill_tc_kernel"], "decode": ["sched_kernel", "fwd_decode_kernel"]},
     }
