@@ -27,8 +27,12 @@ namespace fa {
 namespace dec {
 
 constexpr int TN = 64;                 // keys per scheduler block (metadata unit); a stage holds TNS keys
-constexpr int NCONS = 4;               // consumer warps
-constexpr int NTHREADS = (NCONS + 1) * 32;
+// Consumer warps per CTA.  A 16-bit cache runs one CTA per SM; an e4m3 cache runs TWO (half-size stages): every
+// consumer warp works on every stage, so one CTA's stage rate is bounded by the latency of one warp's
+// ldmatrix -> widen -> MMA -> softmax -> MMA chain, and with twice the keys per byte that chain, not HBM, was the
+// limit; a second CTA's chain runs beside it.
+constexpr int ncons_for(int) { return 4; }
+constexpr int ctas_per_sm(int esz) { return esz == 1 ? 2 : 1; }
 constexpr int HD = 128, HDV = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
@@ -44,7 +48,8 @@ struct DecArgs {
 
 template <int ESZ, int NST>
 struct Smem {
-  static constexpr int TNS = ESZ == 1 ? 128 : 64;   // keys per stage: 32 KB of K+V either way
+  static constexpr int TNS = 64;                    // keys per stage: 32 KB (16-bit) or 16 KB (e4m3) of K+V
+  static constexpr int NC = ncons_for(ESZ);         // consumer warps; 16 keys per warp and stage either way
   static constexpr int kKBytes = TNS * HD * ESZ, kVBytes = TNS * HDV * ESZ;
   static constexpr int kStage = kKBytes + kVBytes;
   static constexpr int kRing = NST * kStage;
@@ -53,7 +58,7 @@ struct Smem {
   static constexpr int kMiscOff = kBarOff + 2 * NST * 8;       // abort flags
   static constexpr int kScrOff = (kMiscOff + 16 + 15) / 16 * 16;
   static constexpr int kLdO = HDV + 4;
-  static constexpr int kScrBytes = NCONS * 16 * kLdO * 4 + 3 * NCONS * 16 * 4;
+  static constexpr int kScrBytes = NC * 16 * kLdO * 4 + 3 * NC * 16 * 4;
   static constexpr int kBytes = kScrOff + kScrBytes;
 };
 
@@ -74,7 +79,8 @@ __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, vol
   }
 }
 
-__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(NCONS * 32) : "memory"); }
+template <int NC>
+__device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(NC * 32) : "memory"); }
 
 struct WorkItem {
   int b, hk, split, lo, hi;   // key-block range [lo, hi) in units of TN keys
@@ -105,15 +111,19 @@ __device__ __forceinline__ WorkItem decode_work(const KParams& p, int w) {
 
 // T = MMA element type (bf16 / fp16); KV8 = the cache holds e4m3 bytes.
 template <typename T, bool KV8, int NST>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__((ncons_for(KV8 ? 1 : 2) + 1) * 32, ctas_per_sm(KV8 ? 1 : 2))
 fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   constexpr int ESZ = KV8 ? 1 : 2;
   using SM = Smem<ESZ, NST>;
-  // 16-bit cache: m16n8k16 MMA in the cache's type.  e4m3 cache: m16n8k32 e4m3 MMA, fp32 accumulate; Q rows are
-  // quantised to e4m3 with a per-row scale (undone in the softmax scale) and P is rounded to e4m3.
-  using TM = T;
+  // 16-bit cache: m16n8k16 MMA in the cache's type.  e4m3 cache: the bytes are widened to fp16 in registers (exact,
+  // one conversion per two elements) and fed to the fp16 m16n8k16 MMA; Q rows are scaled into fp16 range with a
+  // per-row factor (undone in the softmax scale), P is fp16.  (The warp-level e4m3 MMA is not used: on sm_100a
+  // it runs on the fp16 sub-pipe with both operands unpacked again for every instruction, which measured
+  // 4 x the instructions of this path's 16-bit sibling per key.)
+  using TM = typename std::conditional<KV8, __half, T>::type;
   constexpr int TNS = SM::TNS;            // keys per stage
-  constexpr int WK = TNS / NCONS;         // keys per consumer warp and stage (16 or 32)
+  constexpr int NC = SM::NC;
+  constexpr int WK = TNS / NC;            // keys per consumer warp and stage: 16
   constexpr int NT = WK / 8;              // 8-key MMA column tiles per warp
   const KParams& p = a.kp;
   extern __shared__ unsigned char smem_dyn[];
@@ -124,19 +134,19 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
   volatile int* s_info = reinterpret_cast<volatile int*>(sm + SM::kInfoOff);   // 4 ints per stage
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + SM::kMiscOff);
   float* s_o = reinterpret_cast<float*>(sm + SM::kScrOff);
-  float* s_m = s_o + NCONS * 16 * SM::kLdO;
-  float* s_l = s_m + NCONS * 16;
-  float* s_lr = s_l + NCONS * 16;
+  float* s_m = s_o + NC * 16 * SM::kLdO;
+  float* s_l = s_m + NC * 16;
+  float* s_lr = s_l + NC * 16;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    for (int s = 0; s < NST; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, NCONS); }
+    for (int s = 0; s < NST; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, NC); }
     s_abort[0] = 0; s_abort[1] = 0;
     mbar_fence_init();
   }
   __syncthreads();
 
-  if (warp == NCONS) {
+  if (warp == NC) {
     // ============================================ producer ============================================
     if (lane == 0) { tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); }
     uint32_t cnt = 0;
@@ -223,7 +233,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
     const int rep = p.rep;
     uint32_t cnt = 0;
     bool ok = true;
-    uint32_t qf[HD / 16][4];   // 16-bit: 8 k-steps of 16; e4m3: the first 4 entries are 4 k-steps of 32
+    uint32_t qf[HD / 16][4];   // A operand of 8 k-steps of 16
     float qs_a = 1.f, qs_b = 1.f;   // e4m3 Q: 1 / (row quantisation scale), folded into the logit scale
     float o[HDV / 8][4];
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
@@ -262,9 +272,11 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
             }
           }
         } else {
-          // A operand of m16n8k32 (e4m3): a0/a1 = rows g/g+8, columns 32k + 4tq..+3; a2/a3 = columns 32k + 16 + 4tq..+3.
-          // Each row is scaled so that its largest magnitude lands at 224 before rounding to e4m3.
-          float qv[2][HD / 32][2][4];
+          // A operand of m16n8k16 in fp16.  The K bytes reach a lane as 4 consecutive head-dim positions of one key
+          // (see the QK loop), so k-step ks contracts positions 16ks + {4tq, 4tq+1 | 4tq+2, 4tq+3} in its two halves;
+          // Q is gathered in the same order (a sum does not care about the order of its terms).  Each row is
+          // scaled so that its largest magnitude is 256 before conversion to fp16.
+          float qv[2][HD / 16][4];
           float amax[2] = {0.f, 0.f};
 #pragma unroll
           for (int rr = 0; rr < 2; ++rr) {
@@ -274,40 +286,36 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
             const T* qrow = reinterpret_cast<const T*>(p.q) + (int64_t)(it.q0 + (live ? token : 0)) * p.q_row_stride +
                             (int64_t)(live ? head : 0) * p.q_head_stride;
 #pragma unroll
-            for (int k32 = 0; k32 < HD / 32; ++k32)
-#pragma unroll
-              for (int part = 0; part < 2; ++part) {
-                uint2 raw = make_uint2(0u, 0u);
-                if (live) raw = *reinterpret_cast<const uint2*>(qrow + k32 * 32 + part * 16 + 4 * tq);
-                float f[4];
-                if (std::is_same<T, __nv_bfloat16>::value) {
-                  f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);
-                  f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xffff0000u);
-                } else {
-                  const float2 lo2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-                  const float2 hi2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-                  f[0] = lo2.x; f[1] = lo2.y; f[2] = hi2.x; f[3] = hi2.y;
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) { qv[rr][k32][part][j] = f[j]; amax[rr] = fmaxf(amax[rr], fabsf(f[j])); }
+            for (int ks = 0; ks < HD / 16; ++ks) {
+              uint2 raw = make_uint2(0u, 0u);
+              if (live) raw = *reinterpret_cast<const uint2*>(qrow + ks * 16 + 4 * tq);
+              float f[4];
+              if (std::is_same<T, __nv_bfloat16>::value) {
+                f[0] = __uint_as_float(raw.x << 16); f[1] = __uint_as_float(raw.x & 0xffff0000u);
+                f[2] = __uint_as_float(raw.y << 16); f[3] = __uint_as_float(raw.y & 0xffff0000u);
+              } else {
+                const float2 lo2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                const float2 hi2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                f[0] = lo2.x; f[1] = lo2.y; f[2] = hi2.x; f[3] = hi2.y;
               }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) { qv[rr][ks][j] = f[j]; amax[rr] = fmaxf(amax[rr], fabsf(f[j])); }
+            }
           }
 #pragma unroll
           for (int rr = 0; rr < 2; ++rr) {
             amax[rr] = fmaxf(amax[rr], __shfl_xor_sync(0xffffffffu, amax[rr], 1));
             amax[rr] = fmaxf(amax[rr], __shfl_xor_sync(0xffffffffu, amax[rr], 2));
           }
-          const float sq_a = amax[0] > 0.f ? 224.f / amax[0] : 1.f, sq_b = amax[1] > 0.f ? 224.f / amax[1] : 1.f;
+          const float sq_a = amax[0] > 0.f ? 256.f / amax[0] : 1.f, sq_b = amax[1] > 0.f ? 256.f / amax[1] : 1.f;
           qs_a = 1.f / sq_a; qs_b = 1.f / sq_b;
 #pragma unroll
-          for (int k32 = 0; k32 < HD / 32; ++k32)
-#pragma unroll
-            for (int part = 0; part < 2; ++part) {
-              qf[k32][2 * part] = pack4_e4m3(qv[0][k32][part][0] * sq_a, qv[0][k32][part][1] * sq_a,
-                                             qv[0][k32][part][2] * sq_a, qv[0][k32][part][3] * sq_a);
-              qf[k32][2 * part + 1] = pack4_e4m3(qv[1][k32][part][0] * sq_b, qv[1][k32][part][1] * sq_b,
-                                                 qv[1][k32][part][2] * sq_b, qv[1][k32][part][3] * sq_b);
-            }
+          for (int ks = 0; ks < HD / 16; ++ks) {
+            qf[ks][0] = pack2<__half>(qv[0][ks][0] * sq_a, qv[0][ks][1] * sq_a);
+            qf[ks][1] = pack2<__half>(qv[1][ks][0] * sq_b, qv[1][ks][1] * sq_b);
+            qf[ks][2] = pack2<__half>(qv[0][ks][2] * sq_a, qv[0][ks][3] * sq_a);
+            qf[ks][3] = pack2<__half>(qv[1][ks][2] * sq_b, qv[1][ks][3] * sq_b);
+          }
         }
         float sc = p.scale;
         vds = 1.f;
@@ -352,17 +360,22 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
           }
         } else {
           // e4m3 rows are 128 bytes: one swizzle row per key.  ldmatrix moves 16-byte chunks, so lane (g, tq)
-          // receives bytes 4tq..4tq+3 of key g: exactly the B operand of m16n8k32, no conversion needed.
+          // receives bytes 4tq..4tq+3 of key g; widened to two fp16 pairs they are the B operand of one k-step.
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {
+          for (int hf = 0; hf < WK / 16; ++hf) {
             const uint32_t krow = kb + (uint32_t)(warp * WK + hf * 16 + (mat >> 1) * 8 + l7) * 128u;
 #pragma unroll
             for (int k32 = 0; k32 < HD / 32; ++k32) {
               uint32_t raw4[4];
               const uint32_t chunk = (uint32_t)(k32 * 2 + (mat & 1));
               ldmatrix_x4(raw4, krow + ((chunk ^ (uint32_t)l7) << 4));
-              mma_16832_e4m3(sacc[2 * hf], qf[k32], raw4[0], raw4[1]);
-              mma_16832_e4m3(sacc[2 * hf + 1], qf[k32], raw4[2], raw4[3]);
+              uint32_t b[4][2];
+#pragma unroll
+              for (int m = 0; m < 4; ++m) e4m3x4_to<__half>(raw4[m], b[m][0], b[m][1]);
+              mma_16816<__half>(sacc[2 * hf], qf[2 * k32], b[0][0], b[0][1]);
+              mma_16816<__half>(sacc[2 * hf], qf[2 * k32 + 1], b[1][0], b[1][1]);
+              mma_16816<__half>(sacc[2 * hf + 1], qf[2 * k32], b[2][0], b[2][1]);
+              mma_16816<__half>(sacc[2 * hf + 1], qf[2 * k32 + 1], b[3][0], b[3][1]);
             }
           }
         }
@@ -403,24 +416,9 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
           ps_a += sacc[nt][0] + sacc[nt][1];
           ps_b += sacc[nt][2] + sacc[nt][3];
         }
-        uint32_t pa8[4];
-        if constexpr (KV8) {
-          // P as e4m3; the row sums are taken over the ROUNDED probabilities so that numerator and denominator
-          // describe the same weights
-          pa8[0] = pack4_e4m3(sacc[0][0], sacc[0][1], sacc[1][0], sacc[1][1]);
-          pa8[1] = pack4_e4m3(sacc[0][2], sacc[0][3], sacc[1][2], sacc[1][3]);
-          pa8[2] = pack4_e4m3(sacc[2][0], sacc[2][1], sacc[3][0], sacc[3][1]);
-          pa8[3] = pack4_e4m3(sacc[2][2], sacc[2][3], sacc[3][2], sacc[3][3]);
-          auto sum4 = [](uint32_t q4) {
-            const uint32_t h0 = e4m3x2_to_f16x2((uint16_t)(q4 & 0xffffu)), h1 = e4m3x2_to_f16x2((uint16_t)(q4 >> 16));
-            const float2 f = __half22float2(__hadd2(*reinterpret_cast<const __half2*>(&h0), *reinterpret_cast<const __half2*>(&h1)));
-            return f.x + f.y;
-          };
-          lr_a = lr_a * corr_a + sum4(pa8[0]) + sum4(pa8[2]);
-          lr_b = lr_b * corr_b + sum4(pa8[1]) + sum4(pa8[3]);
-        }
         l_a = l_a * corr_a + ps_a;
         l_b = l_b * corr_b + ps_b;
+        if constexpr (KV8) { lr_a = l_a; lr_b = l_b; }   // P is fp16: one sum serves the LSE and the normalisation
         if (__any_sync(0xffffffffu, corr_a != 1.f || corr_b != 1.f)) {
 #pragma unroll
           for (int i = 0; i < HDV / 8; ++i) { o[i][0] *= corr_a; o[i][1] *= corr_a; o[i][2] *= corr_b; o[i][3] *= corr_b; }
@@ -442,26 +440,34 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
             mma_16816<TM>(o[2 * np + 1], pa, bfr[2], bfr[3]);
           }
         } else {
-          // P as the e4m3 A operand of m16n8k32.  This lane holds keys {2tq, 2tq+1} of each 8-key tile; contraction
-          // slots 4tq..4tq+3 take the pairs of tiles 0 and 1, slots 16+4tq.. those of tiles 2 and 3.
-          const uint32_t (&pa)[4] = pa8;
-          // V: the B operand needs 4 KEYS of one value column per register, i.e. bytes of different rows.
+          // P as the fp16 A operand of one k-step of 16 keys.
+          uint32_t pa[4];
+          pa[0] = pack2<__half>(sacc[0][0], sacc[0][1]);
+          pa[1] = pack2<__half>(sacc[0][2], sacc[0][3]);
+          pa[2] = pack2<__half>(sacc[1][0], sacc[1][1]);
+          pa[3] = pack2<__half>(sacc[1][2], sacc[1][3]);
+          // V: the B operand needs pairs of KEYS of one value column per register, i.e. bytes of different rows.
           // ldmatrix.trans on 16-bit units hands lane (g, tq) the byte pairs (columns 2g, 2g+1) of keys 2tq and
-          // 2tq+1 of each 8-key group; one byte permute per register pair gathers the four keys of the even
-          // column and of the odd column, in the same slot order as P above.  Accumulator tile 2c therefore holds
-          // value columns 16c + {0,2,..,14} and tile 2c+1 the odd ones (undone when the result is written out).
-          const uint32_t vrow = vb + (uint32_t)(warp * WK + mat * 8 + l7) * 128u;
+          // 2tq+1 of each 8-key group; one byte permute per register pair gathers, for the even and for the odd
+          // column, keys {2tq, 2tq+1, 8+2tq, 9+2tq}: widened to fp16 these are b0 and b1 of the k-step.
+          // Accumulator tile 2c therefore holds value columns 16c + {0,2,..,14} and tile 2c+1 the odd ones (undone
+          // when the result is written out).  One ldmatrix covers the 16 keys of two 16-column chunks.
+          const uint32_t vrow = vb + (uint32_t)(warp * WK + (mat & 1) * 8 + l7) * 128u;
 #pragma unroll
-          for (int c = 0; c < HDV / 16; ++c) {
+          for (int c2 = 0; c2 < HDV / 32; ++c2) {
             uint32_t r4[4];
-            ldmatrix_x4_trans(r4, vrow + (((uint32_t)c ^ (uint32_t)l7) << 4));
-            uint32_t e0, e1, o0, o1;
-            asm("prmt.b32 %0, %1, %2, 0x6420;" : "=r"(e0) : "r"(r4[0]), "r"(r4[1]));
-            asm("prmt.b32 %0, %1, %2, 0x6420;" : "=r"(e1) : "r"(r4[2]), "r"(r4[3]));
-            asm("prmt.b32 %0, %1, %2, 0x7531;" : "=r"(o0) : "r"(r4[0]), "r"(r4[1]));
-            asm("prmt.b32 %0, %1, %2, 0x7531;" : "=r"(o1) : "r"(r4[2]), "r"(r4[3]));
-            mma_16832_e4m3(o[2 * c], pa, e0, e1);
-            mma_16832_e4m3(o[2 * c + 1], pa, o0, o1);
+            ldmatrix_x4_trans(r4, vrow + (((uint32_t)(2 * c2 + (mat >> 1)) ^ (uint32_t)l7) << 4));
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int c = 2 * c2 + h;
+              uint32_t ev, od, be0, be1, bo0, bo1;
+              asm("prmt.b32 %0, %1, %2, 0x6420;" : "=r"(ev) : "r"(r4[2 * h]), "r"(r4[2 * h + 1]));
+              asm("prmt.b32 %0, %1, %2, 0x7531;" : "=r"(od) : "r"(r4[2 * h]), "r"(r4[2 * h + 1]));
+              e4m3x4_to<__half>(ev, be0, be1);
+              e4m3x4_to<__half>(od, bo0, bo1);
+              mma_16816<__half>(o[2 * c], pa, be0, be1);
+              mma_16816<__half>(o[2 * c + 1], pa, bo0, bo1);
+            }
           }
         }
       }
@@ -496,24 +502,26 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
           s_l[warp * 16 + g] = l_a; s_l[warp * 16 + g + 8] = l_b;
           s_lr[warp * 16 + g] = lr_a; s_lr[warp * 16 + g + 8] = lr_b;
         }
-        bar_consumers();
+        bar_consumers<NC>();
         {
-          const int R = tid >> 3, c0 = (tid & 7) * 16;
+          constexpr int CPT = 16 * HDV / (NC * 32);      // output columns per thread: 16 or 8
+          constexpr int GPR = HDV / CPT;                 // threads per row
+          const int R = tid / GPR, c0 = (tid % GPR) * CPT;
           const int rows_total = it.seqlen_q * rep;
-          float mw[NCONS], M = -INFINITY;
+          float mw[NC], M = -INFINITY;
 #pragma unroll
-          for (int wi = 0; wi < NCONS; ++wi) { mw[wi] = s_m[wi * 16 + R]; M = fmaxf(M, mw[wi]); }
-          float L = 0.f, Lr = 0.f, acc[16];
+          for (int wi = 0; wi < NC; ++wi) { mw[wi] = s_m[wi * 16 + R]; M = fmaxf(M, mw[wi]); }
+          float L = 0.f, Lr = 0.f, acc[CPT];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+          for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
 #pragma unroll
-          for (int wi = 0; wi < NCONS; ++wi) {
+          for (int wi = 0; wi < NC; ++wi) {
             const float e = mw[wi] == -INFINITY ? 0.f : ex2(mw[wi] - M);
             L += e * s_l[wi * 16 + R];
             Lr += e * s_lr[wi * 16 + R];
             const float* src = s_o + (wi * 16 + R) * SM::kLdO + c0;
 #pragma unroll
-            for (int j = 0; j < 16; j += 4) {
+            for (int j = 0; j < CPT; j += 4) {
               const float4 v4 = *reinterpret_cast<const float4*>(src + j);
               acc[j] += e * v4.x; acc[j + 1] += e * v4.y; acc[j + 2] += e * v4.z; acc[j + 3] += e * v4.w;
             }
@@ -526,9 +534,9 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
               const float inv = Ln > 0.f ? vds / Ln : 0.f;
               float* op = p.o_part + (((int64_t)it.split * p.total_q + qi) * p.hq + head) * p.hdv + c0;
 #pragma unroll
-              for (int j = 0; j < 16; j += 4)
+              for (int j = 0; j < CPT; j += 4)
                 *reinterpret_cast<float4*>(op + j) = make_float4(acc[j] * inv, acc[j + 1] * inv, acc[j + 2] * inv, acc[j + 3] * inv);
-              if ((tid & 7) == 0)
+              if (tid % GPR == 0)
                 p.lse_part[((int64_t)it.split * p.hq + head) * p.total_q + qi] = L > 0.f ? (M + lg2(L)) * kLn2 : -INFINITY;
             } else {
               float osc = 1.f;
@@ -543,18 +551,18 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
               const float Ln = KV8 ? Lr : L;
               const float inv = Ln > 0.f ? osc * vds / Ln : 0.f;
               T* op = reinterpret_cast<T*>(p.out) + qi * p.o_row_stride + (int64_t)head * p.o_head_stride + c0;
-              uint4 v0, v1;
-              v0.x = pack2<T>(acc[0] * inv, acc[1] * inv);   v0.y = pack2<T>(acc[2] * inv, acc[3] * inv);
-              v0.z = pack2<T>(acc[4] * inv, acc[5] * inv);   v0.w = pack2<T>(acc[6] * inv, acc[7] * inv);
-              v1.x = pack2<T>(acc[8] * inv, acc[9] * inv);   v1.y = pack2<T>(acc[10] * inv, acc[11] * inv);
-              v1.z = pack2<T>(acc[12] * inv, acc[13] * inv); v1.w = pack2<T>(acc[14] * inv, acc[15] * inv);
-              *reinterpret_cast<uint4*>(op) = v0;
-              *reinterpret_cast<uint4*>(op + 8) = v1;
-              if ((tid & 7) == 0) p.lse[(int64_t)head * p.total_q + qi] = L > 0.f ? (M + lg2(L)) * kLn2 : -INFINITY;
+#pragma unroll
+              for (int j = 0; j < CPT; j += 8) {
+                uint4 v;
+                v.x = pack2<T>(acc[j] * inv, acc[j + 1] * inv);     v.y = pack2<T>(acc[j + 2] * inv, acc[j + 3] * inv);
+                v.z = pack2<T>(acc[j + 4] * inv, acc[j + 5] * inv); v.w = pack2<T>(acc[j + 6] * inv, acc[j + 7] * inv);
+                *reinterpret_cast<uint4*>(op + j) = v;
+              }
+              if (tid % GPR == 0) p.lse[(int64_t)head * p.total_q + qi] = L > 0.f ? (M + lg2(L)) * kLn2 : -INFINITY;
             }
           }
         }
-        bar_consumers();   // the scratch area is free again
+        bar_consumers<NC>();   // the scratch area is free again
       }
     }
   }
@@ -614,9 +622,10 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
   const int smem = SM::kBytes + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
   if (e != cudaSuccess) return (int)e;
-  int grid = a.total_work < pl.num_sms ? a.total_work : pl.num_sms;
+  const int ctas = pl.num_sms * ctas_per_sm(KV8 ? 1 : 2);
+  int grid = a.total_work < ctas ? a.total_work : ctas;
   if (grid <= 0) return 0;
-  kern<<<grid, NTHREADS, smem, stream>>>(a, mk, mv);
+  kern<<<grid, (SM::NC + 1) * 32, smem, stream>>>(a, mk, mv);
   return (int)cudaGetLastError();
 }
 
@@ -637,8 +646,8 @@ int launch_decode(const KParams& kp, const Plan& pl, int compute_dtype, cudaStre
   const int slots = kp.batch * pl.max_mtiles;
   const bool bf = compute_dtype != FA_DT_FP16;
   if (kp.kv_fp8)
-    return bf ? dec::launch_t<__nv_bfloat16, true, 5>(kp, pl, slots, stream)
-              : dec::launch_t<__half, true, 5>(kp, pl, slots, stream);
+    return bf ? dec::launch_t<__nv_bfloat16, true, 4>(kp, pl, slots, stream)
+              : dec::launch_t<__half, true, 4>(kp, pl, slots, stream);
   return bf ? dec::launch_t<__nv_bfloat16, false, 5>(kp, pl, slots, stream)
             : dec::launch_t<__half, false, 5>(kp, pl, slots, stream);
 }
