@@ -69,7 +69,7 @@ struct Smem {
   static constexpr int kKStage = TN * HD * ESZ;
   static constexpr int kVStage = TN * HDV * ESZ;
   static constexpr int kBarOff = kQBytes + KST * kKStage + VST * kVStage;
-  static constexpr int kNumBars = 2 + KST + 2 * VST + 8 + 1 + 4 + 1;
+  static constexpr int kNumBars = 2 + KST + 2 * VST + 8 + 1 + 4 + 1 + KST;
   static constexpr int kItemOff = kBarOff + ((kNumBars * 8 + 16 + 15) & ~15);   // after abort flags and TMEM base
   static constexpr int kBytes = kItemOff + 2 * 64;             // two mailbox slots of one decoded work item each
 };
@@ -177,6 +177,11 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   const uint32_t bar_w_full = bar_drain + 8;             // [2] work id published by the TMA thread
   const uint32_t bar_w_empty = bar_w_full + 16;          // [2] read by the MMA thread and the 8 softmax warps
   const uint32_t bar_k0_full = bar_w_empty + 16;         // K of an item's first block (later K tiles ride on v_full)
+  const uint32_t bar_k_full = bar_k0_full + 8;           // [KST] used instead when the K and V rings differ in depth
+  // With rings of equal depth a later K tile completes on the barrier of the V tile before it (one consumer wait per
+  // block less).  With a single V stage (head_dim 192) that V tile is the late one, and PV must not wait for the
+  // K tile behind it as well: there every K tile has the barrier of its slot.
+  constexpr bool MERGE_KV = KST == VST;
   Item* s_item = reinterpret_cast<Item*>(sm + SM::kItemOff);   // [2]
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + SM::kBarOff + SM::kNumBars * 8);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sm + SM::kBarOff + SM::kNumBars * 8 + 8);
@@ -193,6 +198,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     }
     mbar_init(bar_drain, 1);
     mbar_init(bar_k0_full, 1);
+    for (int s = 0; s < KST; ++s) mbar_init(bar_k_full + 8 * s, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(bar_w_full + 8 * i, 1); mbar_init(bar_w_empty + 8 * i, 9); }
     s_abort[0] = 0;
     s_abort[1] = 0;   // [1] is never raised: waits that may only end by completion or time limit
@@ -280,8 +286,9 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           const uint32_t s = kr.slot;
           ok = wait_or_abort(bar_k_empty + 8 * s, kr.phase ^ 1u, s_abort);
           if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
-          mbar_expect_tx(bar_k0_full, SM::kKStage);
-          load_tile(&map_k, HD, sK + s * SM::kKStage, it.ulo, bar_k0_full);
+          const uint32_t kbar = MERGE_KV ? bar_k0_full : bar_k_full + 8 * s;
+          mbar_expect_tx(kbar, SM::kKStage);
+          load_tile(&map_k, HD, sK + s * SM::kKStage, it.ulo, kbar);
           kr.advance();
           ++k0cnt;
         }
@@ -291,11 +298,13 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           ok = wait_or_abort(bar_v_empty + 8 * vs, vr.phase ^ 1u, s_abort);
           if (ok && nxt) ok = wait_or_abort(bar_k_empty + 8 * ks, kr.phase ^ 1u, s_abort);
           if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
-          mbar_expect_tx(bar_v_full + 8 * vs, SM::kVStage + (nxt ? SM::kKStage : 0));
+          mbar_expect_tx(bar_v_full + 8 * vs, SM::kVStage + ((MERGE_KV && nxt) ? SM::kKStage : 0));
           load_tile(&map_v, HDV, sV + vs * SM::kVStage, nb, bar_v_full + 8 * vs);
           vr.advance();
           if (nxt) {
-            load_tile(&map_k, HD, sK + ks * SM::kKStage, nb + 1, bar_v_full + 8 * vs);
+            const uint32_t kbar = MERGE_KV ? bar_v_full + 8 * vs : bar_k_full + 8 * ks;
+            if constexpr (!MERGE_KV) mbar_expect_tx(kbar, SM::kKStage);
+            load_tile(&map_k, HD, sK + ks * SM::kKStage, nb + 1, kbar);
             kr.advance();
           }
           if (nb == it.ulo) it_next = fetch_and_publish();
@@ -304,7 +313,13 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       if (!ok) *s_abort = 1;
       // drain: every copy this thread issued must have landed before the CTA may leave
       if (qcnt > 0) wait_or_abort(bar_q_full, (qcnt - 1) & 1, s_abort + 1 /* never set: pure time limit */);
-      if (k0cnt > 0) wait_or_abort(bar_k0_full, (k0cnt - 1) & 1, s_abort + 1);
+      if constexpr (MERGE_KV) {
+        if (k0cnt > 0) wait_or_abort(bar_k0_full, (k0cnt - 1) & 1, s_abort + 1);
+      } else {
+        for (uint32_t s = 0; s < (uint32_t)KST; ++s) {
+          if (kr.n > s) { const uint32_t last = (kr.n - 1 - s) / KST; wait_or_abort(bar_k_full + 8 * s, last & 1, s_abort + 1); }
+        }
+      }
       for (uint32_t s = 0; s < (uint32_t)VST; ++s) {
         if (vr.n > s) { const uint32_t last = (vr.n - 1 - s) / VST; wait_or_abort(bar_v_full + 8 * s, last & 1, s_abort + 1); }
       }
@@ -388,7 +403,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       // prologue: QK of the first block
       {
         const uint32_t ks = kr.slot;
-        wait(bar_k0_full, k0cnt & 1);
+        if constexpr (MERGE_KV) wait(bar_k0_full, k0cnt & 1);
+        else wait(bar_k_full + 8 * ks, kr.phase);
         ++k0cnt;
 #pragma unroll
         for (int t = 0; t < 2; ++t)
@@ -401,7 +417,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         const bool nxt = i + 1 < uhi;
         const uint32_t vs = vr.slot;
         const uint32_t ks = kr.slot;          // slot of block i+1 (if any)
-        wait(bar_v_full + 8 * vs, vr.phase);   // V of this block and K of the next one
+        wait(bar_v_full + 8 * vs, vr.phase);   // V of this block (and, with merged barriers, K of the next one)
+        bool k_ready = MERGE_KV;
 #pragma unroll
         for (int t = 0; t < 2; ++t) {
           if (i >= lo[t] && i < hi[t]) {
@@ -416,13 +433,17 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
             ++pcnt[t];
             if (i + 1 == hi[t]) commit(bar_o_full + 8 * t);
           }
-          if (nxt && i + 1 >= lo[t] && i + 1 < hi[t]) issue_qk(t, ks);
+          if (nxt && i + 1 >= lo[t] && i + 1 < hi[t]) {
+            if (!k_ready) { wait(bar_k_full + 8 * ks, kr.phase); k_ready = true; }
+            issue_qk(t, ks);
+          }
         }
         // the item's last QK has been issued: the next item's Q tiles load during this item's last block
         if (i + 2 == uhi) commit(bar_q_empty);
         commit(bar_v_empty + 8 * vs);
         vr.advance();
         if (nxt) {
+          if (!k_ready) wait(bar_k_full + 8 * ks, kr.phase);   // block i+1 belongs to neither tile: still consume its K slot
           commit(bar_k_empty + 8 * ks);
           kr.advance();
         }
