@@ -86,11 +86,11 @@ Plan make_plan(const PlanInput& in) {
   int route = in.route;
   const bool tc_ok = prefill_tc_supported(in) && in.tc_layout_ok, dec_ok = decode_supported(in);
   if (route == FA_ROUTE_AUTO) {
-    if (dec_ok && in.max_seqlen_q * rep <= 16) route = FA_ROUTE_DECODE;
+    if (dec_ok && in.max_seqlen_q * rep <= kDecodeMaxRows) route = FA_ROUTE_DECODE;
     else if (tc_ok) route = FA_ROUTE_PREFILL_TC;
     else route = FA_ROUTE_GENERAL;
   }
-  if ((route == FA_ROUTE_PREFILL_TC && !tc_ok) || (route == FA_ROUTE_DECODE && !(dec_ok && in.max_seqlen_q * rep <= 16))) {
+  if ((route == FA_ROUTE_PREFILL_TC && !tc_ok) || (route == FA_ROUTE_DECODE && !(dec_ok && in.max_seqlen_q * rep <= kDecodeMaxRows))) {
     pl.err = FA_ERR_UNSUPPORTED;
     return pl;
   }

@@ -1,7 +1,8 @@
 // fa_decode.cu — paged-KV decode: a bandwidth-bound streaming kernel.
 //
-// Work item = (batch entry, kv head, split).  The `rep * q_len <= 16` query rows that share one KV head are
-// packed into one 16-row MMA tile, so every K/V byte is read from HBM once per kv head.  Persistent CTAs
+// Work item = (batch entry and 16-row tile, kv head, split).  The `rep * q_len` query rows that share one KV head
+// are packed into 16-row MMA tiles: with up to 16 rows every K/V byte is read from HBM once per kv head, with
+// more rows (up to 64) once per tile.  Persistent CTAs
 // (one per SM) pull work items longest-first from the scheduler metadata through an atomic counter.
 //
 //   warp 4      producer: resolves page-table entries (32 at a time, one coalesced load) and streams whole
@@ -83,7 +84,7 @@ template <int NC>
 __device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(NC * 32) : "memory"); }
 
 struct WorkItem {
-  int b, hk, split, lo, hi;   // key-block range [lo, hi) in units of TN keys
+  int b, mt, hk, split, lo, hi;   // mt: which 16 of the rep*q_len packed rows; key-block range [lo, hi) in units of TN keys
   int seqlen_q, seqlen_k, q0, leftpad;
   bool valid;
 };
@@ -96,6 +97,7 @@ __device__ __forceinline__ WorkItem decode_work(const KParams& p, int w) {
   it.split = rem - it.hk * p.nsplits;
   const int32_t* ent = p.work + kSchedHeader + 4 * e;
   it.b = ent[0];
+  it.mt = ent[1] > 0 ? ent[1] : 0;
   it.valid = it.b >= 0;
   it.lo = it.hi = 0;
   it.seqlen_q = it.seqlen_k = it.q0 = it.leftpad = 0;
@@ -259,7 +261,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
           for (int ks = 0; ks < HD / 16; ++ks) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {      // A operand of m16n8k16: columns ks*16 + 2*tq (+8)
-              const int R = g + (e & 1) * 8;
+              const int R = it.mt * 16 + g + (e & 1) * 8;
               const int c = ks * 16 + 2 * tq + (e >> 1) * 8;
               uint32_t v = 0;
               if (R < rows_total) {
@@ -280,7 +282,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
           float amax[2] = {0.f, 0.f};
 #pragma unroll
           for (int rr = 0; rr < 2; ++rr) {
-            const int R = g + rr * 8;
+            const int R = it.mt * 16 + g + rr * 8;
             const bool live = R < rows_total;
             const int token = R / rep, head = it.hk * rep + R % rep;
             const T* qrow = reinterpret_cast<const T*>(p.q) + (int64_t)(it.q0 + (live ? token : 0)) * p.q_row_stride +
@@ -325,14 +327,15 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         c_mul = has_cap ? p.softcap * kLog2e : sc * kLog2e;
         cap_in = has_cap ? sc / p.softcap : 0.f;
         const int off = it.seqlen_k - it.seqlen_q;
-        const int qp_a = off + g / rep, qp_b = off + (g + 8) / rep;
+        const int rb = it.mt * 16;                   // first packed row of this work item
+        const int qp_a = off + (rb + g) / rep, qp_b = off + (rb + g + 8) / rep;
         lo_a = lo_b = it.leftpad;
         hi_a = hi_b = min(it.seqlen_k, it.hi * TN) - 1;   // keys past this split's range are not ours
         if (p.is_causal) { hi_a = min(hi_a, qp_a); hi_b = min(hi_b, qp_b); }
         if (p.window_right >= 0) { hi_a = min(hi_a, qp_a + p.window_right); hi_b = min(hi_b, qp_b + p.window_right); }
         if (p.window_left >= 0) { lo_a = max(lo_a, qp_a - p.window_left); lo_b = max(lo_b, qp_b - p.window_left); }
         // bounds valid for all 16 rows (rows past rows_total included: conservative)
-        const int qp_lo = off, qp_hi = off + 15 / rep;
+        const int qp_lo = off + rb / rep, qp_hi = off + (rb + 15) / rep;
         lo_max = it.leftpad; hi_min = min(it.seqlen_k, it.hi * TN) - 1;
         if (p.is_causal) hi_min = min(hi_min, qp_lo);
         if (p.window_right >= 0) hi_min = min(hi_min, qp_lo + p.window_right);
@@ -506,20 +509,21 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         {
           constexpr int CPT = 16 * HDV / (NC * 32);      // output columns per thread: 16 or 8
           constexpr int GPR = HDV / CPT;                 // threads per row
-          const int R = tid / GPR, c0 = (tid % GPR) * CPT;
+          const int Rl = tid / GPR, c0 = (tid % GPR) * CPT;   // row within the tile, first column
+          const int R = it.mt * 16 + Rl;                     // packed row (token, head)
           const int rows_total = it.seqlen_q * rep;
           float mw[NC], M = -INFINITY;
 #pragma unroll
-          for (int wi = 0; wi < NC; ++wi) { mw[wi] = s_m[wi * 16 + R]; M = fmaxf(M, mw[wi]); }
+          for (int wi = 0; wi < NC; ++wi) { mw[wi] = s_m[wi * 16 + Rl]; M = fmaxf(M, mw[wi]); }
           float L = 0.f, Lr = 0.f, acc[CPT];
 #pragma unroll
           for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
 #pragma unroll
           for (int wi = 0; wi < NC; ++wi) {
             const float e = mw[wi] == -INFINITY ? 0.f : ex2(mw[wi] - M);
-            L += e * s_l[wi * 16 + R];
-            Lr += e * s_lr[wi * 16 + R];
-            const float* src = s_o + (wi * 16 + R) * SM::kLdO + c0;
+            L += e * s_l[wi * 16 + Rl];
+            Lr += e * s_lr[wi * 16 + Rl];
+            const float* src = s_o + (wi * 16 + Rl) * SM::kLdO + c0;
 #pragma unroll
             for (int j = 0; j < CPT; j += 4) {
               const float4 v4 = *reinterpret_cast<const float4*>(src + j);

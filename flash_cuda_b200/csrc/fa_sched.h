@@ -22,6 +22,9 @@ constexpr int32_t kSchedMagic = 0x46413230;
 constexpr int32_t kSchedVersion = 1;
 constexpr int kSchedHeader = 16;
 constexpr int kSchedSortMax = 8192;
+// The decode route packs the rep*q_len query rows of one kv head into 16-row tiles; each tile is a work item that
+// streams the KV once, so the route is taken while that many passes still beat the other routes.
+constexpr int kDecodeMaxRows = 64;
 
 struct Plan {
   int route;            // FA_ROUTE_* actually taken (never AUTO)

@@ -98,6 +98,9 @@ def decode_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> bool:
     return hq % hkv == 0
 
 
+DECODE_MAX_ROWS = 64   # rep*q_len rows of one kv head, in 16-row tiles (fa_sched.h: kDecodeMaxRows)
+
+
 def make_plan(*, batch, max_seqlen_q, max_seqlen_k, hq, hkv, hd, hdv, q_dtype=DT_BF16, kv_dtype=None, page_size=0,
               num_splits=0, sm_margin=0, route=ROUTE_AUTO, num_sms_device=148, tc_enabled=None,
               decode_enabled=None) -> Plan:
@@ -110,7 +113,7 @@ def make_plan(*, batch, max_seqlen_q, max_seqlen_k, hq, hkv, hd, hdv, q_dtype=DT
     tc_ok = tc_enabled and prefill_tc_supported(**shape)
     dec_ok = decode_enabled and decode_supported(**shape)
     if route == ROUTE_AUTO:
-        if dec_ok and max_seqlen_q * rep <= 16:
+        if dec_ok and max_seqlen_q * rep <= DECODE_MAX_ROWS:
             route = ROUTE_DECODE
         elif tc_ok:
             route = ROUTE_PREFILL_TC

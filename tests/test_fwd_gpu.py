@@ -126,6 +126,28 @@ def test_empty_and_degenerate_sequences(route, cuda_device):
     assert torch.all(out[:24] == 0)
 
 
+@pytest.mark.parametrize("kv_dtype", [None, "fp8"])
+@pytest.mark.parametrize("hq,hkv,q_lens", [
+    (32, 1, [1, 1, 1]),        # MQA: 32 rows per kv head = 2 row tiles
+    (16, 2, [5, 3, 1]),        # speculative decode: up to 40 rows, ragged (the last sequence has 1 tile only)
+    (32, 8, [16, 7, 2]),       # 64 rows = 4 tiles, the most the route takes
+])
+def test_decode_route_with_several_row_tiles(hq, hkv, q_lens, kv_dtype, cuda_device):
+    """rep * q_len above 16: the decode route runs one work item per 16-row tile; splits included."""
+    ctx = [700, 129, 64]
+    p = W.make_problem("decode_tiles", list(zip(q_lens, ctx)), hq=hq, hkv=hkv, hd=128, causal=True, page_size=64,
+                       leftpad=[5, 0, 40], kv_dtype=kv_dtype, sink=True, seed=21)
+    ref_out, ref_lse = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
+    pd = p.to(cuda_device)
+    for nsplits in (1, 3):
+        kw = dict(pd.capi_kw())
+        kw["num_splits"] = nsplits
+        out, lse, _ = capi.fwd(pd.q, pd.k, pd.v, route=capi.FA_ROUTE_DECODE, check=True, **kw)
+        _check(out, lse, ref_out, ref_lse, _tol(p.q, p.k), f"decode_tiles/{hq}/{hkv}/{kv_dtype}/s{nsplits}")
+    out, lse, _ = capi.fwd(pd.q, pd.k, pd.v, check=True, **pd.capi_kw())   # AUTO takes the same route
+    _check(out, lse, ref_out, ref_lse, _tol(p.q, p.k), "decode_tiles/auto")
+
+
 def test_small_shapes_of_benchmark_configs(cuda_device):
     """Each benchmark configuration at a size the oracle finishes in seconds."""
     probs = [
