@@ -635,13 +635,13 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
 
 }  // namespace dec
 
-// Shapes the decode route takes: paged KV, head_dim 128, 16-bit queries, page sizes that are whole TMA boxes.
+// Shapes the decode route takes: paged KV, head_dim 128, 16-bit queries, pages of 16 or 32 keys or whole 64-key TMA boxes.
 bool decode_supported(const PlanInput& in) {
   if (in.q_dtype == FA_DT_FP8_E4M3) return false;
   if (in.kv_dtype != in.q_dtype && in.kv_dtype != FA_DT_FP8_E4M3) return false;
   if (in.hd != 128 || in.hdv != 128) return false;
   const int ps = in.page_size;
-  if (!(ps == 16 || ps == 32 || ps == 64 || ps == 128)) return false;
+  if (!(ps == 16 || ps == 32 || (ps > 0 && ps % 64 == 0))) return false;   // pages divide a 64-row TMA box or are whole boxes
   return in.hkv > 0 && in.hq % in.hkv == 0 && in.tc_layout_ok;
 }
 
