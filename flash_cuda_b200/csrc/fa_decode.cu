@@ -85,7 +85,7 @@ __device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;"
 
 struct WorkItem {
   int b, mt, hk, split, lo, hi;   // mt: which 16 of the rep*q_len packed rows; key-block range [lo, hi) in units of TN keys
-  int seqlen_q, seqlen_k, q0, leftpad;
+  int seqlen_q, seqlen_k, q0, k0, leftpad;   // k0: first row of this sequence in a contiguous (unpaged) K/V
   bool valid;
 };
 
@@ -100,12 +100,13 @@ __device__ __forceinline__ WorkItem decode_work(const KParams& p, int w) {
   it.mt = ent[1] > 0 ? ent[1] : 0;
   it.valid = it.b >= 0;
   it.lo = it.hi = 0;
-  it.seqlen_q = it.seqlen_k = it.q0 = it.leftpad = 0;
+  it.seqlen_q = it.seqlen_k = it.q0 = it.k0 = it.leftpad = 0;
   if (it.valid) {
     split_range(ent[2], ent[3], it.split, p.nsplits, &it.lo, &it.hi);
     it.q0 = p.cu_q[it.b];
     it.seqlen_q = p.cu_q[it.b + 1] - it.q0;
-    it.seqlen_k = p.seqused_k[it.b];
+    it.k0 = p.page_table ? 0 : p.cu_k[it.b];
+    it.seqlen_k = p.seqused_k ? p.seqused_k[it.b] : (p.cu_k[it.b + 1] - p.cu_k[it.b]);
     it.leftpad = p.leftpad_k ? p.leftpad_k[it.b] : 0;
   }
   return it;
@@ -153,7 +154,8 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
     if (lane == 0) { tma_prefetch_desc(&map_k); tma_prefetch_desc(&map_v); }
     uint32_t cnt = 0;
     bool ok = true;
-    const int ps = p.page_size;
+    const bool paged = p.page_table != nullptr;
+    const int ps = paged ? p.page_size : TNS;   // contiguous K/V: "pages" of one stage, at rows k0 + key
     const int boxes = TNS / a.box_rows;         // TMA boxes per stage and 128-byte column block
     while (ok) {
       int w = 0;
@@ -178,7 +180,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
       const int key_end = it.hi * TN;
       for (int key0 = it.lo * TN; key0 < key_end && ok; key0 += TNS) {
         const int lp0 = key0 / ps;              // first logical page of this stage
-        if (cache_first < 0 || lp0 < cache_first || lp0 + boxes > cache_first + 32) {
+        if (paged && (cache_first < 0 || lp0 < cache_first || lp0 + boxes > cache_first + 32)) {
           cache_first = lp0;
           const int lp = lp0 + lane;
           cache_id = lp < npages ? p.page_table[(int64_t)it.b * p.page_table_stride + lp] : -1;
@@ -197,9 +199,10 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         for (int j = 0; j < boxes; ++j) {
           const int kk = key0 + j * a.box_rows;
           const int lp = kk / ps;
-          const int pid = __shfl_sync(0xffffffffu, cache_id, lp - cache_first);
+          const int pid = paged ? __shfl_sync(0xffffffffu, cache_id, lp - cache_first) : 0;
           if (lane == 0) {
-            const int y = (kk < it.seqlen_k && kk < key_end && pid >= 0) ? pid * ps + (kk - lp * ps) : a.kv_total_rows;
+            int y = a.kv_total_rows;                 // out of range: TMA fills zeros
+            if (kk < it.seqlen_k && kk < key_end && pid >= 0) y = paged ? pid * ps + (kk - lp * ps) : it.k0 + kk;
             const uint32_t roff = (uint32_t)(j * a.box_rows) * 128u;
             if (KV8) {
               tma_load_2d(kdst + roff, &map_k, it.hk * HD, y, bar_full + 8 * s);
@@ -615,8 +618,9 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
   a.kp = kp;
   a.total_work = num_work_slots * kp.hkv * kp.nsplits;
   constexpr int TNS = SM::TNS;
-  a.box_rows = kp.page_size < TNS ? kp.page_size : TNS;
-  const uint64_t rows = (uint64_t)kp.num_pages * (uint64_t)kp.page_size;
+  const bool paged = kp.page_table != nullptr;
+  a.box_rows = (paged && kp.page_size < TNS) ? kp.page_size : TNS;
+  const uint64_t rows = paged ? (uint64_t)kp.num_pages * (uint64_t)kp.page_size : (uint64_t)kp.total_k;
   a.kv_total_rows = (int)rows;
   const int kvdt = KV8 ? FA_DT_FP8_E4M3 : (std::is_same<T, __half>::value ? FA_DT_FP16 : FA_DT_BF16);
   CUtensorMap mk, mv;
@@ -635,13 +639,14 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
 
 }  // namespace dec
 
-// Shapes the decode route takes: paged KV, head_dim 128, 16-bit queries, pages of 16 or 32 keys or whole 64-key TMA boxes.
+// Shapes the decode route takes: head_dim 128, 16-bit queries, K/V contiguous or in pages of 16 or 32 keys or whole
+// 64-key TMA boxes.
 bool decode_supported(const PlanInput& in) {
   if (in.q_dtype == FA_DT_FP8_E4M3) return false;
   if (in.kv_dtype != in.q_dtype && in.kv_dtype != FA_DT_FP8_E4M3) return false;
   if (in.hd != 128 || in.hdv != 128) return false;
   const int ps = in.page_size;
-  if (!(ps == 16 || ps == 32 || (ps > 0 && ps % 64 == 0))) return false;   // pages divide a 64-row TMA box or are whole boxes
+  if (!(ps == 0 || ps == 16 || ps == 32 || ps % 64 == 0)) return false;   // pages divide a 64-row TMA box or are whole boxes
   return in.hkv > 0 && in.hq % in.hkv == 0 && in.tc_layout_ok;
 }
 

@@ -93,7 +93,7 @@ def decode_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> bool:
         return False
     if (hd, hdv) != (128, 128):
         return False
-    if not (page_size in (16, 32) or (page_size > 0 and page_size % 64 == 0)):   # whole 64-row TMA boxes, or pages that divide one
+    if not (page_size in (0, 16, 32) or page_size % 64 == 0):   # contiguous, pages that divide a 64-row TMA box, or whole boxes
         return False
     return hq % hkv == 0
 

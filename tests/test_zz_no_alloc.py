@@ -48,8 +48,8 @@ def test_static_scratch_rejects_what_does_not_fit(cuda_device):
     with pytest.raises(capi.FaError) as ei:
         capi.decode_fwd_static(big.q, big.k, big.v, **dict(big.capi_kw(), num_splits=64))
     assert ei.value.code == capi.FA_ERR_STATIC_LIMIT and "8 MiB" in str(ei.value)
-    # a shape the decode route does not take (contiguous KV) is refused, not rerouted
-    dense = W.make_problem("na_dense", [(4, 64)], hq=4, hkv=4, hd=128, seed=25).to(cuda_device)
+    # a shape the decode route does not take (head_dim 64) is refused, not rerouted
+    dense = W.make_problem("na_dense", [(4, 64)], hq=4, hkv=4, hd=64, page_size=64, seed=25).to(cuda_device)
     with pytest.raises(capi.FaError) as ei:
         capi.decode_fwd_static(dense.q, dense.k, dense.v, **dense.capi_kw())
     assert ei.value.code == capi.FA_ERR_UNSUPPORTED
