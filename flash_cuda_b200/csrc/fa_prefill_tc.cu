@@ -48,6 +48,7 @@ struct TcArgs {
   int max_pairs;
   int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128)
   int kv_total_rows; // rows of the K/V tensor map (out-of-range y => zero fill)
+  int out_cols;      // value columns that exist (head_dim 96 runs as 128 with zero-filled columns 96..127)
 };
 
 struct fp8_t { unsigned char x; };   // tag type: Q, K, V and P are e4m3 bytes, the output is bf16
@@ -258,7 +259,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         for (int t = 0; t < 2; ++t)
 #pragma unroll
           for (int cb = 0; cb < HD / EPB; ++cb)
-            tma_load_2d(sQ + t * (TM * HD * ESZ) + cb * (TM * 128), &map_q, it.h * HD + cb * EPB,
+            tma_load_3d(sQ + t * (TM * HD * ESZ) + cb * (TM * 128), &map_q, cb * EPB, it.h,
                         it.q0 + it.pair * 2 * TM + t * TM, bar_q_full);
         ++qcnt;
         const int hk = it.h / p.rep;
@@ -266,7 +267,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         auto load_tile = [&](const CUtensorMap* map, int width, uint32_t dst, int nb, uint32_t bar) {
           if (p.page_table == nullptr) {
             for (int cb = 0; cb < width / EPB; ++cb)
-              tma_load_2d(dst + cb * (TN * 128), map, hk * width + cb * EPB, it.k0 + nb * TN, bar);
+              tma_load_3d(dst + cb * (TN * 128), map, cb * EPB, hk, it.k0 + nb * TN, bar);
           } else {
             for (int r = 0; r < TN; r += a.kv_box_rows) {
               const int kk = nb * TN + r;
@@ -276,7 +277,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
                 y = p.page_table[(int64_t)it.b * p.page_table_stride + lp] * p.page_size + (kk - lp * p.page_size);
               }
               for (int cb = 0; cb < width / EPB; ++cb)
-                tma_load_2d(dst + cb * (TN * 128) + r * 128, map, hk * width + cb * EPB, y, bar);
+                tma_load_3d(dst + cb * (TN * 128) + r * 128, map, cb * EPB, hk, y, bar);
             }
           }
         };
@@ -650,7 +651,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       const bool row_ok = row < it.seqlen_q;
       TO* op = reinterpret_cast<TO*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
 #pragma unroll 1
-      for (int c = 0; c < HDV / 32; ++c) {
+      for (int c = 0; c < a.out_cols / 32; ++c) {
         uint32_t o[32];
         if (had_blocks) {
           tmem_ld32(tO + c * 32, o);
@@ -707,20 +708,21 @@ static EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D map over a row-major [rows, cols] matrix of 16-bit elements, row pitch in elements; box = 64 cols x box_rows.
-static bool make_map_2d(CUtensorMap* m, const void* ptr, int dtype, uint64_t rows, uint64_t cols, uint64_t pitch_elems,
-                        uint32_t box_rows) {
+// 3-D map over [rows][heads][head_dim] (innermost first: column, head, row); box = 128 bytes of one head x box_rows
+// rows.  Columns of a box past head_dim are filled with zeros, which is how head_dim 96 rides on the 128-wide kernel.
+static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t rows, uint64_t heads, uint64_t head_dim,
+                        uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_rows) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
-  const cuuint64_t dims[2] = {cols, rows};
   const uint32_t esz = dtype == FA_DT_FP8_E4M3 ? 1 : 2;
-  const cuuint64_t strides[1] = {pitch_elems * esz};
-  const cuuint32_t box[2] = {128 / esz, box_rows};
-  const cuuint32_t estr[2] = {1, 1};
+  const cuuint64_t dims[3] = {head_dim, heads, rows};
+  const cuuint64_t strides[2] = {head_stride_elems * esz, row_stride_elems * esz};
+  const cuuint32_t box[3] = {128 / esz, 1, box_rows};
+  const cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapDataType dt = dtype == FA_DT_FP8_E4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : dtype == FA_DT_FP16   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  return fn(m, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  return fn(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -735,10 +737,11 @@ static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
   const bool paged = kp.page_table != nullptr;
   a.kv_box_rows = paged ? (kp.page_size < TN ? kp.page_size : TN) : TN;
   a.kv_total_rows = (int)kv_rows;
+  a.out_cols = kp.hdv;
   CUtensorMap mq, mk, mv;
-  if (!make_map_2d(&mq, kp.q, dtype, (uint64_t)kp.total_q, (uint64_t)kp.hq * HD, (uint64_t)kp.q_row_stride, TM)) return -1;
-  if (!make_map_2d(&mk, kp.k, dtype, kv_rows, (uint64_t)kp.hkv * HD, (uint64_t)kp.k_row_stride, a.kv_box_rows)) return -1;
-  if (!make_map_2d(&mv, kp.v, dtype, kv_rows, (uint64_t)kp.hkv * HDV, (uint64_t)kp.v_row_stride, a.kv_box_rows)) return -1;
+  if (!make_map_3d(&mq, kp.q, dtype, (uint64_t)kp.total_q, kp.hq, kp.hd, kp.hd, (uint64_t)kp.q_row_stride, TM)) return -1;
+  if (!make_map_3d(&mk, kp.k, dtype, kv_rows, kp.hkv, kp.hd, kp.hd, (uint64_t)kp.k_row_stride, a.kv_box_rows)) return -1;
+  if (!make_map_3d(&mv, kp.v, dtype, kv_rows, kp.hkv, kp.hdv, kp.hdv, (uint64_t)kp.v_row_stride, a.kv_box_rows)) return -1;
   auto kern = fwd_prefill_tc_kernel<T, HD, HDV, KST, VST>;
   int smem = SM::kBytes + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;   // one CTA per SM: the CTA owns all 512 TMEM columns
@@ -756,7 +759,8 @@ static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
 // back to back) are checked at launch: fa_b200_fwd re-plans onto the general route when they do not hold.
 bool prefill_tc_supported(const PlanInput& in) {
   if (in.q_dtype != in.kv_dtype) return false;
-  const bool hd_ok = (in.hd == 64 && in.hdv == 64) || (in.hd == 128 && in.hdv == 128) || (in.hd == 192 && in.hdv == 128);
+  const bool hd_ok = (in.hd == 64 && in.hdv == 64) || (in.hd == 128 && in.hdv == 128) || (in.hd == 192 && in.hdv == 128) ||
+                     (in.hd == 96 && in.hdv == 96);   // 96 runs as 128: TMA zero-fills columns 96..127
   if (!hd_ok) return false;
   if (in.q_dtype == FA_DT_FP8_E4M3 && !(in.hd == 128 && in.hdv == 128)) return false;   // e4m3: head_dim 128 only
   if (in.page_size > 0) {
@@ -782,7 +786,7 @@ int launch_prefill_tc(const KParams& kp, const Plan& pl, int dtype, cudaStream_t
   const bool bf = dtype != FA_DT_FP16;
   if (kp.q_fp8 && kp.kv_fp8)
     return kp.hd == 128 && kp.hdv == 128 ? tc::launch_impl<tc::fp8_t, 128, 128, 4, 4>(kp, pl, FA_DT_FP8_E4M3, kv_rows, stream) : -1;
-  if (kp.hd == 128 && kp.hdv == 128)
+  if ((kp.hd == 128 && kp.hdv == 128) || (kp.hd == 96 && kp.hdv == 96))
     return bf ? tc::launch_impl<__nv_bfloat16, 128, 128, 2, 2>(kp, pl, dtype, kv_rows, stream)
               : tc::launch_impl<__half, 128, 128, 2, 2>(kp, pl, dtype, kv_rows, stream);
   if (kp.hd == 64 && kp.hdv == 64)

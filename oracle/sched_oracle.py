@@ -79,7 +79,7 @@ class Plan:
 def prefill_tc_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> bool:
     if q_dtype != kv_dtype:
         return False
-    if (hd, hdv) not in ((64, 64), (128, 128), (192, 128)):
+    if (hd, hdv) not in ((64, 64), (96, 96), (128, 128), (192, 128)):
         return False
     if q_dtype == DT_FP8 and (hd, hdv) != (128, 128):
         return False
