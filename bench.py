@@ -7,11 +7,15 @@
 
 Headline workload (`config.workload`): causal GQA prefill, bf16, B=4, Hq=32, Hkv=8, S=4096, head_dim 128
 (seeded N(0,1) inputs, softmax scale 1/sqrt(128)); metric = prefill TFLOP/s, algorithmic FLOPs
-2*(hd+hdv)*Hq*unmasked_pairs.  A second object, `decode`, reports the paged-KV decode workload (batch 128,
-context 1k..32k, page 64, leftpad 0..63, bf16 KV) as achieved HBM GB/s.
+2*(hd+hdv)*Hq*unmasked_pairs.  Further objects of the same JSON line report the other benchmark configurations:
+`c1` (dense non-causal, latency), `c2_fp8` (the headline in e4m3), `c3` (varlen + window + softcap + sink),
+`decode` / `decode_fp8` (paged decode, batch 128, context 1k..32k, page 64, leftpad 0..63, bf16 / e4m3 cache, as
+achieved HBM GB/s) and `c5` (long context: q 4096 x paged KV 524288, hd192/128, KV range sharded over the GPUs).
 
-For N > 1 the (batch, kv-head) work items are independent, so every rank runs its own batch (weak scaling,
-no collective on the data path); value = total FLOPs of all ranks / max-over-ranks device time.
+For N > 1 the headline is ONE shared problem of N x 4 sequences whose kv heads are sharded over the ranks by
+`multi_gpu.fwd_head_sharded` (per-GPU work = the 1-GPU configuration: weak scaling, no collective);
+value = total FLOPs / max-over-ranks device time.  `c5` is strong scaling through `multi_gpu.fwd_kv_sharded`
+(one all-gather of the partial results + the merge kernel inside the timed region).
 """
 from __future__ import annotations
 
@@ -188,8 +192,35 @@ def _tensor_bytes(*ts):
     return int(sum(t.numel() * t.element_size() for t in ts if t is not None))
 
 
+def _repeat_batch(p, n):
+    """The problem with its batch repeated n times (contiguous K/V, equal lengths): the shared problem of an
+    n-GPU run, identical on every rank."""
+    from dataclasses import replace
+    if n == 1:
+        return p
+    B = len(p.q_lens)
+    cu = lambda lens: torch.tensor([0] + list(torch.tensor(lens * n).cumsum(0).tolist()), dtype=torch.int32,
+                                   device=p.q.device)
+    rep = lambda t: None if t is None else t.repeat(n, *([1] * (t.dim() - 1)))
+    return replace(p, q=rep(p.q), k=rep(p.k), v=rep(p.v), cu_seqlens_q=cu(p.q_lens), cu_seqlens_k=cu(p.k_lens),
+                   q_descale=rep(p.q_descale), k_descale=rep(p.k_descale), v_descale=rep(p.v_descale),
+                   q_lens=p.q_lens * n, k_lens=p.k_lens * n, name=f"{p.name}_x{n}")
+
+
+def _tensor_roofline(tflops, peaks, dtype="bf16", sustained=False):
+    """Tensor-bound roofline object.  The fp8 peak is DERIVED: twice the measured bf16 figure (the tensor cores'
+    e4m3 rate is twice their bf16 rate); no fp8 GEMM was measured on this pool."""
+    base = peaks["bf16_tflops_sustained"] if sustained else peaks["bf16_tflops"]
+    peak = 2.0 * base if dtype == "fp8" else base
+    src = peaks["source"] + (" (sustained: step of hundreds of ms)" if sustained else " (burst)")
+    if dtype == "fp8":
+        src += ", fp8 peak derived as 2 x bf16"
+    return {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+            "peak_source": src}
+
+
 def run_ours(args) -> None:
-    from flash_cuda_b200 import capi, ops, workloads as W
+    from flash_cuda_b200 import capi, multi_gpu as MG, ops, workloads as W
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -205,21 +236,28 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local_rank)
     ops.load(build_if_missing=False)
     peaks = _peaks()
+    warm = max(args.warmup, 3)
 
-    # ---- prefill workload: R rotating copies so that no step re-reads lines a recent step left in L2 ----
-    host = W.causal_gqa_prefill(seed=rank, B=args.batch).pin()
-    flops = host.flops()
+    # ---- headline: causal GQA prefill.  One SHARED problem of world x B sequences (the B-sequence batch of the
+    # benchmark configuration repeated `world` times, identical on every rank); each rank computes its block of
+    # kv heads through multi_gpu.fwd_head_sharded, so per-GPU work is that of the 1-GPU configuration (weak
+    # scaling) and there is no collective.  R rotating copies: no step re-reads lines a recent step left in L2.
+    host = W.causal_gqa_prefill(seed=0, B=args.batch)
+    flops = host.flops()                       # per GPU: world x B sequences x (32 / world) heads
     R = 4
-    sets = [host.to(dev) for _ in range(R)]
-    outs = [torch.empty(host.q.shape[0], host.q.shape[1], host.v.shape[-1], device=dev, dtype=torch.bfloat16)
+    from dataclasses import replace
+    first = _repeat_batch(host.to(dev), world)
+    sets = [first] + [replace(first, q=first.q.clone(), k=first.k.clone(), v=first.v.clone()) for _ in range(R - 1)]
+    hq_loc = host.q.shape[1] // world
+    outs = [torch.empty(sets[0].q.shape[0], hq_loc, host.v.shape[-1], device=dev, dtype=torch.bfloat16)
             for _ in range(R)]
     in_bytes = _tensor_bytes(host.q, host.k, host.v)
 
     def step(i):
         p = sets[i % R]
-        ops.call_fwd(p.q, p.k, p.v, out=outs[i % R], **p.capi_kw())
+        MG.fwd_head_sharded(p.q, p.k, p.v, rank=rank, world=world, out=outs[i % R], **p.capi_kw())
 
-    for i in range(max(args.warmup, 3)):
+    for i in range(warm):
         step(i)
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -231,15 +269,20 @@ def run_ours(args) -> None:
     per_gpu = flops / (ms * 1e-3) / 1e12
 
     # ---- end to end: pinned host inputs -> device, op, result -> pinned host, all inside the timed region ----
-    # Every step copies its inputs from pinned host memory and reads its result back.  The three legs of a step run
-    # on three streams (copy-in, the op on the current stream, copy-out) with two buffer sets, so step i+1's inputs
-    # travel while step i computes and step i-1's result travels back; events order the legs of one step and
-    # protect each buffer until its previous user is done.
+    # Every step copies this rank's shard (its heads of every sequence) from pinned host memory and reads its
+    # result back.  The three legs of a step run on three streams (copy-in, the op on the current stream, copy-out)
+    # with two buffer sets, so step i+1's inputs travel while step i computes and step i-1's result travels back;
+    # events order the legs of one step and protect each buffer until its previous user is done.
     e2e = None
     if not args.no_e2e:
+        qs, ks = MG.head_slice(host.q.shape[1], host.k.shape[1], rank, world)
+        hq_h = host.q[:, qs, :].repeat(world, 1, 1).contiguous().pin_memory()
+        hk_h = host.k[:, ks, :].repeat(world, 1, 1).contiguous().pin_memory()
+        hv_h = host.v[:, ks, :].repeat(world, 1, 1).contiguous().pin_memory()
         s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         cur = torch.cuda.current_stream(dev)
-        dbuf = [(torch.empty_like(sets[0].q), torch.empty_like(sets[0].k), torch.empty_like(sets[0].v)) for _ in range(2)]
+        dbuf = [(torch.empty(hq_h.shape, device=dev, dtype=hq_h.dtype), torch.empty(hk_h.shape, device=dev, dtype=hk_h.dtype),
+                 torch.empty(hv_h.shape, device=dev, dtype=hv_h.dtype)) for _ in range(2)]
         obuf = [torch.empty_like(outs[0]) for _ in range(2)]
         h_out = [torch.empty(outs[0].shape, dtype=outs[0].dtype).pin_memory() for _ in range(2)]
         kw = dict(sets[0].capi_kw())
@@ -253,9 +296,9 @@ def run_ours(args) -> None:
                 with torch.cuda.stream(s_in):
                     if ev_op[b] is not None:
                         s_in.wait_event(ev_op[b])          # the op two steps back has read these inputs
-                    dbuf[b][0].copy_(host.q, non_blocking=True)
-                    dbuf[b][1].copy_(host.k, non_blocking=True)
-                    dbuf[b][2].copy_(host.v, non_blocking=True)
+                    dbuf[b][0].copy_(hq_h, non_blocking=True)
+                    dbuf[b][1].copy_(hk_h, non_blocking=True)
+                    dbuf[b][2].copy_(hv_h, non_blocking=True)
                     ev_in[b] = torch.cuda.Event()
                     ev_in[b].record(s_in)
                 cur.wait_event(ev_in[b])
@@ -290,10 +333,63 @@ def run_ours(args) -> None:
             dist.barrier()
             e2e_ms = float(tt.item())
         e2e = {"value": flops * world / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": _tensor_bytes(h_out[0]),
+               "h2d_bytes_per_step": _tensor_bytes(hq_h, hk_h, hv_h), "d2h_bytes_per_step": _tensor_bytes(h_out[0]),
                "overlap": "copy-in, op and copy-out of consecutive steps on three streams, two buffer sets"}
+        del dbuf, obuf, h_out, hq_h, hk_h, hv_h
+    del sets, outs
+    torch.cuda.empty_cache()
 
-    # ---- decode workload (secondary objects: bf16 KV cache, and e4m3 KV cache with --decode-fp8) ----
+    # ---- the other benchmark configurations, one object each (every rank runs its own copy; per-GPU figures,
+    # `value` = per-GPU figure x ranks) ----
+    def timed_leg(make, steps, rotate, work, unit_scale, extra):
+        """make() -> problem on the host; `rotate` device copies are cycled so that no step finds its inputs in L2
+        (or the one copy is larger than L2)."""
+        try:
+            p0 = make().to(dev)
+            ps = [p0] + [replace(p0, q=p0.q.clone(), k=p0.k.clone(), v=p0.v.clone()) for _ in range(rotate - 1)]
+            os_ = [torch.empty(p.q.shape[0], p.q.shape[1], p.v.shape[-1], device=dev, dtype=torch.bfloat16) for p in ps]
+            kws = [p.capi_kw() for p in ps]
+
+            def leg_step(i):
+                j = i % rotate
+                ops.call_fwd(ps[j].q, ps[j].k, ps[j].v, out=os_[j], **kws[j])
+
+            for i in range(warm):
+                leg_step(i)
+            lms = _time_steps(leg_step, steps, dist, world)
+            res = {"ms_per_step": lms, "steps": steps, "work_per_step": work(ps[0]), "per_gpu": work(ps[0]) / (lms * 1e-3) / unit_scale}
+            res.update(extra(ps[0], res))
+            del ps, os_
+            torch.cuda.empty_cache()
+            return res
+        except Exception as e:  # reported, never hidden
+            torch.cuda.empty_cache()
+            return {"error": repr(e)}
+
+    nsteps = max(3, min(args.steps, 100))
+    legs = {}
+    if not args.headline_only:
+        # C1: dense non-causal B=2 H=8 S=512 (8 MB per copy: 32 rotating copies = 268 MB > L2); a latency figure
+        legs["c1"] = timed_leg(lambda: W.dense_noncausal(seed=0), nsteps, 32, lambda p: p.flops(), 1e12,
+                               lambda p, r: {"workload": "dense non-causal MHA bf16 B=2 H=8 S=512 d=128", "us_per_step": r["ms_per_step"] * 1e3,
+                                             "unit": "TFLOP/s", "roofline": _tensor_roofline(r["per_gpu"], peaks),
+                                             "kernels_per_step": ["fwd_prefill_tc_kernel"], "l2": "32 rotating copies (268 MB)",
+                                             "note": "32 work items on 148 SMs: launch- and latency-bound, the TFLOP/s figure is informational"})
+        # C2 in e4m3 (per-tensor descale)
+        legs["c2_fp8"] = timed_leg(lambda: W.causal_gqa_prefill(seed=0, B=args.batch, dtype="fp8"), nsteps, 4,
+                                   lambda p: p.flops(), 1e12,
+                                   lambda p, r: {"workload": f"causal GQA prefill e4m3 (Q, K, V; per-tensor descale) B={args.batch} Hq=32 Hkv=8 S=4096 d=128",
+                                                 "unit": "TFLOP/s", "roofline": _tensor_roofline(r["per_gpu"], peaks, "fp8"),
+                                                 "kernels_per_step": ["fwd_prefill_tc_kernel (kind::f8f6f4)"], "l2": "4 rotating copies"})
+        # C3: varlen + window + softcap + sink (468 MB of Q alone: larger than L2)
+        legs["c3"] = timed_leg(lambda: W.varlen_window_softcap_sink(seed=0), max(3, min(args.steps, 30)), 1,
+                               lambda p: p.flops(), 1e12,
+                               lambda p, r: {"workload": "varlen packed causal prefill bf16, 16 sequences 128..8192, Hq=32 Hkv=8 d=128, window 4096, softcap 30, sink",
+                                             "unit": "TFLOP/s", "roofline": _tensor_roofline(r["per_gpu"], peaks),
+                                             "kernels_per_step": ["fwd_prefill_tc_kernel"], "l2": "inputs (0.7 GB) larger than L2",
+                                             "note": "one tanh and one exp2 per score share the special-function unit"})
+
+    # ---- decode workload: bf16 KV cache and e4m3 KV cache ----
     def decode_leg(kv_dtype):
         try:
             dp = W.paged_decode_on_device(dev, seed=rank, kv_dtype=kv_dtype)   # the 8.5 GB pool is drawn on the GPU
@@ -304,11 +400,11 @@ def run_ours(args) -> None:
             def dstep(i):
                 ops.call_fwd(dp.q, dp.k, dp.v, out=dout, **dp.capi_kw())
 
-            for i in range(max(args.warmup, 3)):
+            for i in range(warm):
                 dstep(i)
-            dms = _time_steps(dstep, max(3, min(args.steps, 100)), dist, world)
+            dms = _time_steps(dstep, nsteps, dist, world)
             gbs = kvb / (dms * 1e-3) / 1e9
-            return {
+            res = {
                 "metric": f"paged decode HBM GB/s (B=128 q_len=1 ctx 1k..32k page 64 Hq=32 Hkv=8 d=128 {kv_dtype} KV, "
                           "leftpad 0..63)",
                 "value": gbs * world, "unit": "GB/s", "ms_per_step": dms, "kv_bytes_per_step": kvb,
@@ -317,33 +413,54 @@ def run_ours(args) -> None:
                              "frac": gbs / peaks["hbm_gbs"], "traffic": NCU_DECODE_TRAFFIC[kv_dtype],
                              "traffic_source": "ncu dram__bytes_read+write per launch of this configuration (profiles/)",
                              "peak_source": peaks["source"]},
+                "kernels_per_step": ["sched_kernel", "fwd_decode_kernel"],
                 "l2": f"KV pool ({kvb / 1e9:.2f} GB) larger than L2",
             }
+            del dp, dout
+            torch.cuda.empty_cache()
+            return res
         except Exception as e:  # reported, never hidden
+            torch.cuda.empty_cache()
             return {"error": repr(e)}
 
-    decode = None if args.no_decode else decode_leg("bf16")
-    decode_fp8 = decode_leg("fp8") if args.decode_fp8 else None
+    decode = None if (args.no_decode or args.headline_only) else decode_leg("bf16")
+    decode_fp8 = None if (args.no_decode or args.headline_only) else decode_leg("fp8")
+
+    # ---- long context (C5): KV range sharded over the ranks, strong scaling, through multi_gpu.fwd_kv_sharded ----
+    longctx = None
+    if not (args.no_longctx or args.headline_only):
+        try:
+            longctx = _longctx_leg(args, dist, rank, world, dev, peaks)
+        except Exception as e:
+            torch.cuda.empty_cache()
+            longctx = {"error": repr(e)}
 
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
+    for name, leg in legs.items():
+        if "per_gpu" in leg:
+            leg["value"] = leg["per_gpu"] * world
     cpu = cpu_baseline() if (world == 1 and not args.no_cpu) else None
     line = {
         "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded N(0,1), random-permuted page table for decode)",
         "config": {"workload": f"causal GQA prefill B={args.batch} Hq=32 Hkv=8 S=4096 d=128 bf16 per GPU",
-                   "parallelism": f"(batch, kv-head) items sharded over {world} GPU(s), no collective",
-                   "l2": f"{R} rotating input sets of {in_bytes / 1e6:.0f} MB each (> L2 {L2_BYTES / 1e6:.0f} MB)",
+                   "parallelism": (f"one shared problem of {world}x{args.batch} sequences; the 8 kv heads (and their q heads) "
+                                   f"sharded over {world} GPU(s) by multi_gpu.fwd_head_sharded, no collective"),
+                   "global_batch": world * args.batch,
+                   "l2": f"{R} rotating input sets of {in_bytes * world / 1e6:.0f} MB each (> L2 {L2_BYTES / 1e6:.0f} MB)",
                    "flops_per_step_per_gpu": flops},
         "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": per_gpu / peaks["bf16_tflops"], "traffic": NCU_PREFILL_TRAFFIC_PER_BATCH * args.batch,
                      "traffic_source": "ncu dram__bytes_read+write of a B=2 launch, scaled by B (profiles/)",
                      "peak_source": peaks["source"], "kernel": "fwd_prefill_tc_kernel", "launch_ms": ms},
-        "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks, "decode": decode, "decode_fp8": decode_fp8, "cpu_baseline": cpu,
+        "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks, "decode": decode, "decode_fp8": decode_fp8,
+        "c1": legs.get("c1"), "c2_fp8": legs.get("c2_fp8"), "c3": legs.get("c3"), "c5": longctx, "longctx": longctx,
+        "cpu_baseline": cpu,
         "kernels_per_step": {"prefill": ["fwd_prefill_tc_kernel"], "decode": ["sched_kernel", "fwd_decode_kernel"]},
     }
     print(json.dumps(line))
@@ -351,12 +468,53 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
-def run_longctx(args) -> None:
-    """`--workload longctx`: B=1, a chunk of 4096 query rows against a paged KV of 524288 tokens (page 64),
-    128 heads, head_dim 192 / head_dim_v 128, causal, bf16.  The key range is split evenly over the ranks
-    (strong scaling); partial O / LSE are merged with ONE all-gather + the merge kernel, inside the timed region."""
-    from flash_cuda_b200 import multi_gpu as MG, ops, workloads as W
+def _longctx_leg(args, dist, rank, world, dev, peaks, merge="all_gather"):
+    """B=1, a chunk of 4096 query rows against a paged KV of 524288 tokens (page 64), 128 heads, head_dim 192 /
+    head_dim_v 128, causal, bf16.  The key range is split evenly over the ranks (strong scaling); each rank's kernel
+    writes its fp32 partial into the gather buffer, ONE all-gather + the merge kernel finish the step, all inside
+    the timed region; the time between the end of the attention kernel and the end of the merge is reported apart."""
+    from flash_cuda_b200 import multi_gpu as MG, workloads as W
+    q_len, k_len, heads = 4096, args.longctx_keys, 128
+    per = k_len // world
+    p = W.long_context(dev, seed=0, q_len=q_len, k_len=k_len, heads=heads, k_begin=rank * per, k_end=(rank + 1) * per)
+    pairs = q_len * (k_len - q_len) + q_len * (q_len + 1) // 2     # unmasked pairs per head of the WHOLE problem
+    flops = 2.0 * (192 + 128) * heads * pairs
+    marks = []
 
+    def step(i, rec=None):
+        MG.fwd_kv_sharded(p.q, p.k, p.v, page_table_local=p.page_table, seqused_k_local=p.seqused_k,
+                          cu_seqlens_q=p.cu_seqlens_q, max_seqlen_q=q_len, max_seqlen_k_local=per,
+                          softmax_scale=p.softmax_scale, causal=True, rank=rank, world=world, merge=merge, marks=rec)
+
+    for i in range(2):
+        step(i)
+    steps = max(1, min(args.steps, 3))
+    ms = _time_steps(lambda i: step(i, marks), steps, dist, world)
+    merge_ms = 0.0
+    if world > 1:
+        merge_ms = sum(marks[2 * i].elapsed_time(marks[2 * i + 1]) for i in range(steps)) / steps
+        t = torch.tensor([merge_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        merge_ms = float(t.item())
+    val = flops / (ms * 1e-3) / 1e12
+    kvgb = (p.k.numel() + p.v.numel()) * 2 / 1e9
+    del p
+    torch.cuda.empty_cache()
+    return {"metric": "long-context prefill TFLOP/s, whole job (q 4096 x paged KV 524288, 128 heads, hd192/hdv128, causal, bf16)",
+            "value": val, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps, "scaling": "strong",
+            "gather_and_merge_ms": merge_ms, "gather_and_merge_frac": merge_ms / ms if ms > 0 else None,
+            "parallelism": (f"KV range split over {world} GPU(s) by multi_gpu.fwd_kv_sharded; fp32 partials written into the "
+                            f"gather buffer by the kernel, one all-gather (in place), merge kernel reads it in place"
+                            if merge == "all_gather" else
+                            f"KV range split over {world} GPU(s); partial rows exchanged by all-to-all, merged per row block, result all-gathered"),
+            "roofline": _tensor_roofline(val / world, peaks, sustained=True),
+            "kernels_per_step": ["fwd_prefill_tc_kernel"] + ([] if world == 1 else ["ncclAllGather (NCCL)", "combine_kernel"]),
+            "l2": f"KV shard {kvgb:.1f} GB per GPU (> L2)"}
+
+
+def run_longctx(args) -> None:
+    """`--workload longctx`: only the long-context leg (see _longctx_leg), as the headline of its own JSON line."""
+    from flash_cuda_b200 import ops
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -369,40 +527,17 @@ def run_longctx(args) -> None:
     dev = torch.device("cuda", local_rank)
     ops.load(build_if_missing=False)
     peaks = _peaks()
-    q_len, k_len, heads = 4096, args.longctx_keys, 128
-    per = k_len // world
-    p = W.long_context(dev, seed=0, q_len=q_len, k_len=k_len, heads=heads, k_begin=rank * per, k_end=(rank + 1) * per)
-    # unmasked pairs per head of the WHOLE problem: sum_i (k_len - q_len + i + 1)
-    pairs = q_len * (k_len - q_len) + q_len * (q_len + 1) // 2
-    flops = 2.0 * (192 + 128) * heads * pairs
-
-    def step(i):
-        MG.fwd_kv_sharded(p.q, p.k, p.v, page_table_local=p.page_table, seqused_k_local=p.seqused_k,
-                          cu_seqlens_q=p.cu_seqlens_q, max_seqlen_q=q_len, max_seqlen_k_local=per,
-                          softmax_scale=p.softmax_scale, causal=True, rank=rank, world=world)
-
-    for i in range(max(args.warmup, 3)):
-        step(i)
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    steps = max(1, min(args.steps, 10))
-    ms = _time_steps(step, steps, dist, world)
+    leg = _longctx_leg(args, dist, rank, world, dev, peaks, merge=args.longctx_merge)
     clocks = sampler.stop() if rank == 0 else {}
     if rank == 0:
-        val = flops / (ms * 1e-3) / 1e12
-        print(json.dumps({
-            "metric": "long-context prefill TFLOP/s (q 4096 x paged KV 524288, 128 heads, hd192/hdv128, causal, bf16), whole job",
-            "value": val, "unit": "TFLOP/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (N(0,1) drawn on the device, seeded)",
-            "config": {"workload": f"long-context prefill q={q_len} k={k_len} heads={heads} hd192/hdv128 page 64",
-                       "parallelism": f"KV range split over {world} GPU(s); one all-gather of [O|LSE] + merge kernel",
-                       "l2": f"KV shard {p.k.numel() * 2 / 1e9 + p.v.numel() * 2 / 1e9:.1f} GB per GPU (> L2)"},
-            "roofline": {"bound": "tensor", "achieved": val / world, "peak": peaks["bf16_tflops_sustained"],
-                         "unit": "TFLOP/s", "frac": val / world / peaks["bf16_tflops_sustained"], "traffic": None,
-                         "peak_source": peaks["source"] + " (sustained: seconds-long step)"},
-            "gpu_launches": steps * (1 if world == 1 else 2), "clocks": clocks}))
+        print(json.dumps(dict(leg, n_gpus=world, warmup=2, higher_is_better=True, vs_baseline=None, dtype="bf16",
+                              data="synthetic (N(0,1) drawn on the device, seeded)",
+                              config={"workload": f"long-context prefill q=4096 k={args.longctx_keys} heads=128 hd192/hdv128 page 64",
+                                      "merge": args.longctx_merge},
+                              gpu_launches=leg["steps"] * (1 if world == 1 else 2), clocks=clocks)))
     if world > 1:
         dist.destroy_process_group()
 
@@ -413,8 +548,10 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-decode", action="store_true", help="skip the decode workload")
-    ap.add_argument("--decode-fp8", action="store_true", help="also time the decode workload with an e4m3 KV cache")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode workloads")
+    ap.add_argument("--no-longctx", action="store_true", help="skip the long-context (KV-sharded) leg")
+    ap.add_argument("--headline-only", action="store_true", help="only the headline prefill leg (profiler captures)")
+    ap.add_argument("--longctx-merge", default="all_gather", choices=["all_gather", "all_to_all"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--batch", type=int, default=4, help="prefill batch per GPU (4 = the benchmark configuration; "

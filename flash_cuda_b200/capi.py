@@ -16,15 +16,17 @@ from . import build as _build
 
 FA_OK, FA_ERR_UNSUPPORTED, FA_ERR_BAD_ARG, FA_ERR_WORKSPACE, FA_ERR_NO_DEVICE, FA_ERR_LAUNCH, FA_ERR_DEVICE_TIMEOUT = range(7)
 FA_ERR_STATIC_LIMIT = 7
+FA_ERR_BAD_METADATA = 8
 STATIC_SCRATCH_BYTES = 8 << 20
-FA_DT_BF16, FA_DT_FP16, FA_DT_FP8_E4M3 = 0, 1, 2
+FA_DT_BF16, FA_DT_FP16, FA_DT_FP8_E4M3, FA_DT_FP32 = 0, 1, 2, 3
+FA_FLAG_WORKSPACE_CLEAN = 1
 FA_ROUTE_AUTO, FA_ROUTE_PREFILL_TC, FA_ROUTE_DECODE, FA_ROUTE_GENERAL = 0, 1, 2, 3
 
 EXPORTS = (
     "fa_b200_fwd_workspace_bytes", "fa_b200_fwd", "fa_b200_num_splits", "fa_b200_scheduler_metadata_len",
     "fa_b200_get_scheduler_metadata", "fa_b200_combine", "fa_b200_check_status", "fa_b200_strerror",
     "fa_b200_last_cuda_error", "fa_b200_version", "fa_b200_sizeof_fwd_params", "fa_b200_sizeof_sched_params",
-    "fa_b200_decode_fwd_static",
+    "fa_b200_decode_fwd_static", "fa_b200_combine_strided", "fa_b200_selftest_timeout",
 )
 
 _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
@@ -41,7 +43,8 @@ class FaFwdParams(C.Structure):
                                "max_seqlen_k", "page_size", "num_pages", "page_table_stride",
                                "descale_batch_stride", "descale_head_stride", "q_dtype", "kv_dtype", "out_dtype")]
         + [("softmax_scale", _f32), ("softcap", _f32)]
-        + [(n, _i32) for n in ("is_causal", "window_left", "window_right", "num_splits", "sm_margin", "route")]
+        + [(n, _i32) for n in ("is_causal", "window_left", "window_right", "num_splits", "sm_margin", "route",
+                               "scheduler_metadata_len", "flags")]
     )
 
 
@@ -84,6 +87,11 @@ def load(build_if_missing: bool = True):
     lib.fa_b200_get_scheduler_metadata.argtypes = [C.POINTER(FaSchedParams), _vp, _vp]
     lib.fa_b200_combine.restype = C.c_int
     lib.fa_b200_combine.argtypes = [_vp, _vp, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _i64, _i32, _vp, _vp]
+    lib.fa_b200_combine_strided.restype = C.c_int
+    lib.fa_b200_combine_strided.argtypes = [_vp, _vp, _i64, _i64, _i32, _i32, _i32, _i32, _vp, _vp, _i64, _i64, _i32,
+                                            _vp, _vp]
+    lib.fa_b200_selftest_timeout.restype = C.c_int
+    lib.fa_b200_selftest_timeout.argtypes = [_vp, _i64, _vp]
     lib.fa_b200_check_status.restype = C.c_int
     lib.fa_b200_check_status.argtypes = [_vp, _vp, C.POINTER(C.c_uint32)]
     lib.fa_b200_strerror.restype = C.c_char_p
@@ -118,6 +126,8 @@ def dtype_code(dt: torch.dtype) -> int:
         return FA_DT_FP16
     if dt == torch.float8_e4m3fn:
         return FA_DT_FP8_E4M3
+    if dt == torch.float32:
+        return FA_DT_FP32          # output only
     raise ValueError(f"unsupported dtype {dt}")
 
 
@@ -133,7 +143,7 @@ def make_params(q, k, v, out, lse, *, cu_seqlens_q, cu_seqlens_k=None, seqused_k
                 leftpad_k=None, q_descale=None, k_descale=None, v_descale=None, s_aux=None,
                 scheduler_metadata=None, max_seqlen_q, max_seqlen_k, softmax_scale, causal,
                 window_left=-1, window_right=-1, softcap=0.0, num_splits=0, sm_margin=0,
-                route=FA_ROUTE_AUTO):
+                route=FA_ROUTE_AUTO, flags=0):
     """Fills an FaFwdParams from torch tensors.  Returns (params, keepalive list)."""
     keep = []
     paged = page_table is not None
@@ -174,6 +184,8 @@ def make_params(q, k, v, out, lse, *, cu_seqlens_q, cu_seqlens_k=None, seqused_k
         keep.append(sf)
         p.s_aux = sf.data_ptr()
     p.scheduler_metadata = _ptr(scheduler_metadata)
+    p.scheduler_metadata_len = 0 if scheduler_metadata is None else scheduler_metadata.numel()
+    p.flags = int(flags)
     p.max_seqlen_q, p.max_seqlen_k = int(max_seqlen_q), int(max_seqlen_k)
     p.q_dtype, p.kv_dtype, p.out_dtype = dtype_code(q.dtype), dtype_code(k.dtype), dtype_code(out.dtype)
     p.softmax_scale, p.softcap = float(softmax_scale), float(softcap)
@@ -182,18 +194,21 @@ def make_params(q, k, v, out, lse, *, cu_seqlens_q, cu_seqlens_k=None, seqused_k
     return p, keep
 
 
-def fwd(q, k, v, *, out=None, workspace=None, check=False, **kw):
+def fwd(q, k, v, *, out=None, lse=None, workspace=None, check=False, **kw):
     """Attention forward through `fa_b200_fwd`.  Returns (out, lse, workspace).
 
     `kw` are the keyword arguments of make_params.  With check=True the stream is synchronised and the
-    device status word is read (raises FaError on a device-side timeout)."""
+    device status word is read (raises FaError on a device-side timeout or refused metadata).  `out` may be a
+    float32 tensor (the normalised result in fp32: the form of a partial result before a merge); `out` and `lse`
+    may be views into a larger buffer."""
     lib = load()
     total_q, hq, _ = q.shape
     hdv = v.shape[-1]
     out_dtype = torch.bfloat16 if q.dtype == torch.float8_e4m3fn else q.dtype
     if out is None:
         out = torch.empty(total_q, hq, hdv, device=q.device, dtype=out_dtype)
-    lse = torch.empty(hq, total_q, device=q.device, dtype=torch.float32)
+    if lse is None:
+        lse = torch.empty(hq, total_q, device=q.device, dtype=torch.float32)
     p, keep = make_params(q, k, v, out, lse, **kw)
     need = lib.fa_b200_fwd_workspace_bytes(C.byref(p))
     if workspace is None or workspace.numel() < need:
@@ -270,15 +285,45 @@ def get_scheduler_metadata(device, **kw) -> torch.Tensor:
 
 def combine(o_part: torch.Tensor, lse_part: torch.Tensor, s_aux: Optional[torch.Tensor] = None,
             out_dtype: torch.dtype = torch.bfloat16):
-    """LSE-weighted merge of partials: o_part (S, total_q, hq, hdv) fp32, lse_part (S, hq, total_q) fp32."""
+    """LSE-weighted merge of partials: o_part (S, total_q, hq, hdv) fp32, lse_part (S, hq, total_q) fp32.
+    Each split must be contiguous inside; the distance between splits is free (views into a gathered buffer of
+    packed [O | LSE] partials are merged where they lie, through `fa_b200_combine_strided`)."""
     lib = load()
     S, total_q, hq, hdv = o_part.shape
-    assert o_part.is_contiguous() and lse_part.is_contiguous() and o_part.dtype == torch.float32
+    assert o_part.dtype == torch.float32 and lse_part.dtype == torch.float32
+    assert o_part[0].is_contiguous() and lse_part[0].is_contiguous() and lse_part.shape == (S, hq, total_q)
+    o_ss = o_part.stride(0) if S > 1 else total_q * hq * hdv
+    l_ss = lse_part.stride(0) if S > 1 else hq * total_q
     out = torch.empty(total_q, hq, hdv, device=o_part.device, dtype=out_dtype)
     lse = torch.empty(hq, total_q, device=o_part.device, dtype=torch.float32)
     sf = None if s_aux is None else s_aux.to(torch.float32).contiguous()
-    rc = lib.fa_b200_combine(o_part.data_ptr(), lse_part.data_ptr(), S, total_q, hq, hdv, _ptr(sf), out.data_ptr(),
-                             out.stride(0), out.stride(1), dtype_code(out_dtype), lse.data_ptr(), _stream())
+    rc = lib.fa_b200_combine_strided(o_part.data_ptr(), lse_part.data_ptr(), o_ss, l_ss, S, total_q, hq, hdv,
+                                     _ptr(sf), out.data_ptr(), out.stride(0), out.stride(1), dtype_code(out_dtype),
+                                     lse.data_ptr(), _stream())
     if rc != FA_OK:
         raise FaError(rc, "combine")
     return out, lse
+
+
+def partial_layout(total_q: int, hq: int, hdv: int):
+    """(floats of O, floats of one packed partial): [O (total_q, hq, hdv) | LSE (hq, total_q) | pad to 4 floats]."""
+    n_o = total_q * hq * hdv
+    return n_o, n_o + (hq * total_q + 3) // 4 * 4
+
+
+def partial_buffer(total_q: int, hq: int, hdv: int, device):
+    """One packed fp32 buffer [O | LSE] and the two views `fwd(..., out=o_view, lse=lse_view)` writes into."""
+    n_o, per = partial_layout(total_q, hq, hdv)
+    buf = torch.empty(per, device=device, dtype=torch.float32)
+    return buf, buf[:n_o].view(total_q, hq, hdv), buf[n_o:n_o + hq * total_q].view(hq, total_q)
+
+
+def selftest_timeout(device, max_cycles: int = 200_000) -> torch.Tensor:
+    """Launches the bounded-wait self-test (a wait that must give up by itself); returns the workspace whose status
+    word `check_status` then reads."""
+    lib = load()
+    ws = torch.empty(256, device=device, dtype=torch.uint8)
+    rc = lib.fa_b200_selftest_timeout(ws.data_ptr(), int(max_cycles), _stream())
+    if rc != FA_OK:
+        raise FaError(rc, "selftest_timeout")
+    return ws

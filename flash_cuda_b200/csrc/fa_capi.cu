@@ -13,7 +13,11 @@
 
 namespace fa {
 
-int launch_sched(const FaSchedParams& sp, const Plan& pl, int32_t* out_dev, cudaStream_t stream);
+int launch_sched(const FaSchedParams& sp, const Plan& pl, int32_t* out_dev, int32_t* zero_words, cudaStream_t stream);
+int launch_selftest_timeout(DeviceStatus* status, long long max_cycles, cudaStream_t stream);
+int launch_combine_strided(const float* o_part, const float* lse_part, int64_t o_split_stride, int64_t lse_split_stride,
+                           int nsplits, int total_q, int hq, int hdv, const float* s_aux, void* out,
+                           int64_t o_row_stride, int64_t o_head_stride, int out_dtype, float* lse, cudaStream_t stream);
 int launch_decode(const KParams& kp, const Plan& pl, int compute_dtype, cudaStream_t stream);
 int launch_prefill_tc(const KParams& kp, const Plan& pl, int compute_dtype, cudaStream_t stream);
 bool prefill_tc_supported(const PlanInput& in);
@@ -134,7 +138,8 @@ static PlanInput plan_input(const FaFwdParams* p, int num_sms) {
   in.is_causal = p->is_causal; in.window_left = p->window_left; in.window_right = p->window_right;
   normalize_window(in.is_causal, in.max_seqlen_k, &in.window_left, &in.window_right);
   in.has_softcap = p->softcap > 0.f;
-  in.num_splits = p->num_splits; in.sm_margin = p->sm_margin; in.route = p->route;
+  in.num_splits = p->out_dtype == FA_DT_FP32 ? 1 : p->num_splits;   // fp32 output is itself the partial form
+  in.sm_margin = p->sm_margin; in.route = p->route;
   in.num_sms_device = num_sms;
   in.tc_layout_ok = prefill_tc_layout_ok(p) ? 1 : 0;
   return in;
@@ -194,7 +199,7 @@ static int validate(const FaFwdParams* p) {
   const bool q8 = p->q_dtype == FA_DT_FP8_E4M3, kv8 = p->kv_dtype == FA_DT_FP8_E4M3;
   if (p->q_dtype < 0 || p->q_dtype > 2 || p->kv_dtype < 0 || p->kv_dtype > 2) return FA_ERR_BAD_ARG;
   if (!kv8 && p->kv_dtype != p->q_dtype) return FA_ERR_UNSUPPORTED;          // bf16 Q with fp16 KV etc.
-  if (p->out_dtype != (q8 ? FA_DT_BF16 : p->q_dtype)) return FA_ERR_UNSUPPORTED;
+  if (p->out_dtype != FA_DT_FP32 && p->out_dtype != (q8 ? FA_DT_BF16 : p->q_dtype)) return FA_ERR_UNSUPPORTED;
   if (p->hd % 8 || p->hdv % 8) return FA_ERR_UNSUPPORTED;
   const int64_t strides[] = {p->q_row_stride, p->q_head_stride, p->k_row_stride, p->k_head_stride,
                              p->v_row_stride, p->v_head_stride, p->o_row_stride, p->o_head_stride,
@@ -225,6 +230,7 @@ const char* fa_b200_strerror(int code) {
     case FA_ERR_LAUNCH: return "CUDA call failed";
     case FA_ERR_DEVICE_TIMEOUT: return "a device-side wait timed out";
     case FA_ERR_STATIC_LIMIT: return "problem needs more scratch than the 8 MiB built into fa_b200_decode_fwd_static";
+    case FA_ERR_BAD_METADATA: return "scheduler_metadata does not belong to this problem (length or header mismatch)";
     default: return "unknown error";
   }
 }
@@ -258,9 +264,19 @@ int fa_b200_fwd(const FaFwdParams* p, void* workspace, size_t workspace_bytes, f
   if (!workspace || workspace_bytes < w.total || ((uintptr_t)workspace % 256)) return FA_ERR_WORKSPACE;
   if (p->total_q == 0 || p->batch == 0) return FA_OK;
 
+  if (p->scheduler_metadata && p->scheduler_metadata_len > 0 && p->scheduler_metadata_len != sched_len(pl, p->batch))
+    return FA_ERR_BAD_METADATA;
+
   char* ws = (char*)workspace;
-  cudaError_t ce = cudaMemsetAsync(ws, 0, w.header, stream);
-  if (ce != cudaSuccess) return cuda_fail(ce, "cudaMemsetAsync(workspace header)");
+  // The header (status word, work counters) must be zero when the kernels start.  A caller that keeps it clean
+  // (FA_FLAG_WORKSPACE_CLEAN) saves the memset: the kernels leave the counters at zero when they finish.
+  const bool clean = (p->flags & FA_FLAG_WORKSPACE_CLEAN) != 0;
+  // (on the decode route without caller metadata the work-list kernel runs first and clears the header itself)
+  const bool sched_first = pl.route == FA_ROUTE_DECODE && p->scheduler_metadata == nullptr;
+  if (!clean && !sched_first) {
+    cudaError_t ce = cudaMemsetAsync(ws, 0, w.header, stream);
+    if (ce != cudaSuccess) return cuda_fail(ce, "cudaMemsetAsync(workspace header)");
+  }
 
   KParams kp{};
   kp.q = p->q; kp.k = p->k; kp.v = p->v; kp.out = p->out; kp.lse = p->lse;
@@ -287,6 +303,8 @@ int fa_b200_fwd(const FaFwdParams* p, void* workspace, size_t workspace_bytes, f
   kp.q_fp8 = p->q_dtype == FA_DT_FP8_E4M3; kp.kv_fp8 = p->kv_dtype == FA_DT_FP8_E4M3;
   kp.is_causal = in.is_causal; kp.window_left = in.window_left; kp.window_right = in.window_right;
   kp.nsplits = pl.nsplits;
+  kp.out_f32 = p->out_dtype == FA_DT_FP32;
+  kp.work_expect = SchedExpect{p->batch, pl.nsplits, pl.tile_m, pl.tile_n, pl.max_mtiles, pl.rows_per_token, pl.route};
   kp.scale = p->softmax_scale; kp.softcap = p->softcap;
   if (pl.nsplits > 1) { kp.lse_part = (float*)(ws + w.lse_off); kp.o_part = (float*)(ws + w.o_off); }
 
@@ -300,13 +318,15 @@ int fa_b200_fwd(const FaFwdParams* p, void* workspace, size_t workspace_bytes, f
       sp.leftpad_k = p->leftpad_k; sp.batch = p->batch; sp.max_seqlen_q = p->max_seqlen_q;
       sp.max_seqlen_k = p->max_seqlen_k; sp.hq = p->hq; sp.hkv = p->hkv; sp.hd = p->hd; sp.hdv = p->hdv;
       sp.is_causal = in.is_causal; sp.window_left = in.window_left; sp.window_right = in.window_right;
-      rc = note_cuda_error(launch_sched(sp, pl, (int32_t*)(ws + w.work_off), stream), "sched_kernel");
+      rc = note_cuda_error(launch_sched(sp, pl, (int32_t*)(ws + w.work_off), clean ? nullptr : (int32_t*)ws, stream),
+                           "sched_kernel");
       if (rc != FA_OK) return rc;
       work = (const int32_t*)(ws + w.work_off);
     }
     kp.work = work;
     rc = note_cuda_error(launch_decode(kp, pl, compute_dtype, stream), "decode kernel");
   } else if (pl.route == FA_ROUTE_PREFILL_TC) {
+    kp.work = p->scheduler_metadata;   // optional: the sorted (batch, tile) list replaces the arithmetic order
     rc = note_cuda_error(launch_prefill_tc(kp, pl, compute_dtype, stream), "tcgen05 prefill kernel");
   } else {
     rc = note_cuda_error(launch_general(kp, compute_dtype, p->out_dtype, pl.num_sms, stream), "general kernel");
@@ -371,7 +391,7 @@ int fa_b200_get_scheduler_metadata(const FaSchedParams* p, int32_t* out_dev, fa_
   if (pl.err != FA_OK) return pl.err;
   FaSchedParams sp = *p;
   sp.window_left = in.window_left; sp.window_right = in.window_right;
-  return note_cuda_error(launch_sched(sp, pl, out_dev, (cudaStream_t)stream), "sched_kernel");
+  return note_cuda_error(launch_sched(sp, pl, out_dev, nullptr, (cudaStream_t)stream), "sched_kernel");
 }
 
 int fa_b200_combine(const float* o_part, const float* lse_part, int32_t nsplits, int32_t total_q, int32_t hq,
@@ -387,6 +407,33 @@ int fa_b200_combine(const float* o_part, const float* lse_part, int32_t nsplits,
                          "combine kernel");
 }
 
+int fa_b200_combine_strided(const float* o_part, const float* lse_part, int64_t o_split_stride,
+                            int64_t lse_split_stride, int32_t nsplits, int32_t total_q, int32_t hq, int32_t hdv,
+                            const float* s_aux, void* out, int64_t o_row_stride, int64_t o_head_stride,
+                            int32_t out_dtype, float* lse, fa_stream_t stream) {
+  if (!o_part || !lse_part || !out || !lse || nsplits < 1 || hdv % 4 || o_row_stride % 4 || o_head_stride % 4 ||
+      o_split_stride % 4 || ((uintptr_t)o_part % 16))
+    return FA_ERR_BAD_ARG;
+  if (out_dtype != FA_DT_BF16 && out_dtype != FA_DT_FP16) return FA_ERR_UNSUPPORTED;
+  const DevInfo* di = device_info();
+  if (!di || !di->ok) return FA_ERR_NO_DEVICE;
+  return note_cuda_error(launch_combine_strided(o_part, lse_part, o_split_stride, lse_split_stride, nsplits, total_q,
+                                                hq, hdv, s_aux, out, o_row_stride, o_head_stride, out_dtype, lse,
+                                                (cudaStream_t)stream),
+                         "combine kernel");
+}
+
+int fa_b200_selftest_timeout(void* workspace, int64_t max_cycles, fa_stream_t stream_) {
+  if (!workspace || ((uintptr_t)workspace % 16)) return FA_ERR_BAD_ARG;
+  const DevInfo* di = device_info();
+  if (!di || !di->ok) return FA_ERR_NO_DEVICE;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  cudaError_t ce = cudaMemsetAsync(workspace, 0, 256, stream);
+  if (ce != cudaSuccess) return cuda_fail(ce, "cudaMemsetAsync(workspace header)");
+  long long c = max_cycles < 10000 ? 10000 : (max_cycles > 100000000 ? 100000000 : max_cycles);
+  return note_cuda_error(launch_selftest_timeout((DeviceStatus*)workspace, c, stream), "self-test kernel");
+}
+
 int fa_b200_check_status(void* workspace, fa_stream_t stream, uint32_t* detail) {
   if (!workspace) return FA_ERR_BAD_ARG;
   cudaError_t e = cudaStreamSynchronize((cudaStream_t)stream);
@@ -395,7 +442,8 @@ int fa_b200_check_status(void* workspace, fa_stream_t stream, uint32_t* detail) 
   e = cudaMemcpy(&st, workspace, sizeof(st), cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) return cuda_fail(e, "cudaMemcpy(status)");
   if (detail) *detail = st.detail;
-  return st.error == 0 ? FA_OK : FA_ERR_DEVICE_TIMEOUT;
+  if (st.error == 0) return FA_OK;
+  return st.error == DEV_ERR_BAD_INDEX ? FA_ERR_BAD_METADATA : FA_ERR_DEVICE_TIMEOUT;
 }
 
 }  // extern "C"

@@ -18,6 +18,7 @@
 // (kernels/fa4_blackwell.cu:8774-9103, 9605-9993), with per-batch leftpad and fp8 KV (descale folded in).
 #include <cuda.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "fa_internal.h"
@@ -34,7 +35,6 @@ constexpr int TN = 64;                 // keys per scheduler block (metadata uni
 // limit; a second CTA's chain runs beside it.
 constexpr int ncons_for(int) { return 4; }
 constexpr int ctas_per_sm(int esz) { return esz == 1 ? 2 : 1; }
-constexpr int HD = 128, HDV = 128;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 enum Role : unsigned { ROLE_PRODUCER = 5, ROLE_CONSUMER = 6 };
@@ -47,7 +47,7 @@ struct DecArgs {
   int kv_total_rows;
 };
 
-template <int ESZ, int NST>
+template <int ESZ, int NST, int HD, int HDV>
 struct Smem {
   static constexpr int TNS = 64;                    // keys per stage: 32 KB (16-bit) or 16 KB (e4m3) of K+V
   static constexpr int NC = ncons_for(ESZ);         // consumer warps; 16 keys per warp and stage either way
@@ -63,23 +63,6 @@ struct Smem {
   static constexpr int kBytes = kScrOff + kScrBytes;
 };
 
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  // common case: a few probes (each probe already sleeps in hardware until the phase flips or a short time passes)
-#pragma unroll 1
-  for (int i = 0; i < 256; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  // slow case: keep probing; look at the abort flag and the SM clock only every 64 probes (about 2 s at 2 GHz)
-  const long long t0 = clock64();
-#pragma unroll 1
-  while (true) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > 4000000000ll) return false;
-  }
-}
-
 template <int NC>
 __device__ __forceinline__ void bar_consumers() { asm volatile("bar.sync 1, %0;" ::"n"(NC * 32) : "memory"); }
 
@@ -87,8 +70,11 @@ struct WorkItem {
   int b, mt, hk, split, lo, hi;   // mt: which 16 of the rep*q_len packed rows; key-block range [lo, hi) in units of TN keys
   int seqlen_q, seqlen_k, q0, k0, leftpad;   // k0: first row of this sequence in a contiguous (unpaged) K/V
   bool valid;
+  bool bad;     // the entry names a batch or a key range that this problem does not have
 };
 
+// Entry e of the work list -> work item.  The list may come from the caller: an entry is used only if its batch
+// index and key-block range lie inside this problem (else `bad`, and nothing is dereferenced with it).
 __device__ __forceinline__ WorkItem decode_work(const KParams& p, int w) {
   WorkItem it;
   const int per_entry = p.hkv * p.nsplits;
@@ -99,25 +85,31 @@ __device__ __forceinline__ WorkItem decode_work(const KParams& p, int w) {
   it.b = ent[0];
   it.mt = ent[1] > 0 ? ent[1] : 0;
   it.valid = it.b >= 0;
+  it.bad = false;
   it.lo = it.hi = 0;
   it.seqlen_q = it.seqlen_k = it.q0 = it.k0 = it.leftpad = 0;
   if (it.valid) {
-    split_range(ent[2], ent[3], it.split, p.nsplits, &it.lo, &it.hi);
+    if (it.b >= p.batch || it.mt >= p.work_expect.max_mtiles) { it.valid = false; it.bad = true; return it; }
     it.q0 = p.cu_q[it.b];
     it.seqlen_q = p.cu_q[it.b + 1] - it.q0;
     it.k0 = p.page_table ? 0 : p.cu_k[it.b];
     it.seqlen_k = p.seqused_k ? p.seqused_k[it.b] : (p.cu_k[it.b + 1] - p.cu_k[it.b]);
     it.leftpad = p.leftpad_k ? p.leftpad_k[it.b] : 0;
+    const int n_lo = ent[2], n_hi = ent[3];
+    if (n_lo < 0 || n_hi < n_lo || (int64_t)n_hi * TN > (int64_t)it.seqlen_k + TN - 1) { it.valid = false; it.bad = true; return it; }
+    split_range(n_lo, n_hi, it.split, p.nsplits, &it.lo, &it.hi);
   }
   return it;
 }
 
 // T = MMA element type (bf16 / fp16); KV8 = the cache holds e4m3 bytes.
-template <typename T, bool KV8, int NST>
+template <typename T, bool KV8, int NST, int HD, int HDV>
 __global__ void __launch_bounds__((ncons_for(KV8 ? 1 : 2) + 1) * 32, ctas_per_sm(KV8 ? 1 : 2))
 fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   constexpr int ESZ = KV8 ? 1 : 2;
-  using SM = Smem<ESZ, NST>;
+  static_assert(!KV8 || (HD == 128 && HDV == 128), "an e4m3 cache row must fill one 128-byte swizzle row");
+  static_assert(HD % 64 == 0 && HDV % 64 == 0, "whole 128-byte column blocks");
+  using SM = Smem<ESZ, NST, HD, HDV>;
   // 16-bit cache: m16n8k16 MMA in the cache's type.  e4m3 cache: the bytes are widened to fp16 in registers (exact,
   // one conversion per two elements) and fed to the fp16 m16n8k16 MMA; Q rows are scaled into fp16 range with a
   // per-row factor (undone in the softmax scale), P is fp16.  (The warp-level e4m3 MMA is not used: on sm_100a
@@ -157,12 +149,25 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
     const bool paged = p.page_table != nullptr;
     const int ps = paged ? p.page_size : TNS;   // contiguous K/V: "pages" of one stage, at rows k0 + key
     const int boxes = TNS / a.box_rows;         // TMA boxes per stage and 128-byte column block
+    // the list's header must describe this call before any entry is read
+    int total_work = a.total_work;
+    if (!sched_header_matches(p.work, p.work_expect)) {
+      if (lane == 0) report_error(p.status, DEV_ERR_BAD_INDEX, ROLE_PRODUCER);
+      total_work = 0;
+    }
+    bool first_ticket = true;
     while (ok) {
       int w = 0;
-      if (lane == 0) w = atomicAdd(p.counters, 1);
-      w = __shfl_sync(0xffffffffu, w, 0);
-      if (w >= a.total_work) break;
+      if (first_ticket) w = (int)blockIdx.x;     // a CTA's first work id is its block index, later ones are tickets
+      else if (lane == 0) w = (int)gridDim.x + atomicAdd(p.counters, 1);
+      if (!first_ticket) w = __shfl_sync(0xffffffffu, w, 0);
+      first_ticket = false;
+      if (w >= total_work) break;
       const WorkItem it = decode_work(p, w);
+      if (it.bad) {
+        if (lane == 0) report_error(p.status, DEV_ERR_BAD_INDEX, ROLE_PRODUCER);
+        break;
+      }
       if (!it.valid) continue;
       if (it.lo >= it.hi) {   // nothing to stream: one descriptor-only stage so that the output still gets written
         const uint32_t s = cnt % NST;
@@ -209,10 +214,11 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
               tma_load_2d(vdst + roff, &map_v, it.hk * HDV, y, bar_full + 8 * s);
             } else {
 #pragma unroll
-              for (int cb = 0; cb < 2; ++cb) {
+              for (int cb = 0; cb < HD / 64; ++cb)
                 tma_load_2d(kdst + cb * (TNS * 128) + roff, &map_k, it.hk * HD + cb * 64, y, bar_full + 8 * s);
+#pragma unroll
+              for (int cb = 0; cb < HDV / 64; ++cb)
                 tma_load_2d(vdst + cb * (TNS * 128) + roff, &map_v, it.hk * HDV + cb * 64, y, bar_full + 8 * s);
-              }
             }
           }
         }
@@ -231,6 +237,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
     if (lane == 0) {
       for (uint32_t s = 0; s < (uint32_t)NST; ++s)
         if (cnt > s) wait_or_abort(bar_full + 8 * s, ((cnt - 1 - s) / NST) & 1, s_abort + 1);
+      counters_release(p.counters);   // this CTA takes no more tickets
     }
   } else {
     // ============================================ consumers ===========================================
@@ -325,6 +332,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         float sc = p.scale;
         vds = 1.f;
         const int di = it.b * p.descale_batch_stride + it.hk * p.descale_head_stride;
+        if (p.q_descale) sc *= p.q_descale[di];
         if (p.k_descale) sc *= p.k_descale[di];
         if (p.v_descale) vds = p.v_descale[di];
         c_mul = has_cap ? p.softcap * kLog2e : sc * kLog2e;
@@ -557,13 +565,20 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
               }
               const float Ln = KV8 ? Lr : L;
               const float inv = Ln > 0.f ? osc * vds / Ln : 0.f;
-              T* op = reinterpret_cast<T*>(p.out) + qi * p.o_row_stride + (int64_t)head * p.o_head_stride + c0;
+              if (p.out_f32) {
+                float* of = reinterpret_cast<float*>(p.out) + qi * p.o_row_stride + (int64_t)head * p.o_head_stride + c0;
 #pragma unroll
-              for (int j = 0; j < CPT; j += 8) {
-                uint4 v;
-                v.x = pack2<T>(acc[j] * inv, acc[j + 1] * inv);     v.y = pack2<T>(acc[j + 2] * inv, acc[j + 3] * inv);
-                v.z = pack2<T>(acc[j + 4] * inv, acc[j + 5] * inv); v.w = pack2<T>(acc[j + 6] * inv, acc[j + 7] * inv);
-                *reinterpret_cast<uint4*>(op + j) = v;
+                for (int j = 0; j < CPT; j += 4)
+                  *reinterpret_cast<float4*>(of + j) = make_float4(acc[j] * inv, acc[j + 1] * inv, acc[j + 2] * inv, acc[j + 3] * inv);
+              } else {
+                T* op = reinterpret_cast<T*>(p.out) + qi * p.o_row_stride + (int64_t)head * p.o_head_stride + c0;
+#pragma unroll
+                for (int j = 0; j < CPT; j += 8) {
+                  uint4 v;
+                  v.x = pack2<T>(acc[j] * inv, acc[j + 1] * inv);     v.y = pack2<T>(acc[j + 2] * inv, acc[j + 3] * inv);
+                  v.z = pack2<T>(acc[j + 4] * inv, acc[j + 5] * inv); v.w = pack2<T>(acc[j + 6] * inv, acc[j + 7] * inv);
+                  *reinterpret_cast<uint4*>(op + j) = v;
+                }
               }
               if (tid % GPR == 0) p.lse[(int64_t)head * p.total_q + qi] = L > 0.f ? (M + lg2(L)) * kLn2 : -INFINITY;
             }
@@ -611,9 +626,9 @@ static bool make_map(CUtensorMap* m, const void* ptr, int dtype, uint64_t rows, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T, bool KV8, int NST>
+template <typename T, bool KV8, int NST, int HD, int HDV>
 static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaStream_t stream) {
-  using SM = Smem<KV8 ? 1 : 2, NST>;
+  using SM = Smem<KV8 ? 1 : 2, NST, HD, HDV>;
   DecArgs a;
   a.kp = kp;
   a.total_work = num_work_slots * kp.hkv * kp.nsplits;
@@ -626,10 +641,16 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
   CUtensorMap mk, mv;
   if (!make_map(&mk, kp.k, kvdt, rows, (uint64_t)kp.hkv * HD, (uint64_t)kp.k_row_stride, a.box_rows)) return -1;
   if (!make_map(&mv, kp.v, kvdt, rows, (uint64_t)kp.hkv * HDV, (uint64_t)kp.v_row_stride, a.box_rows)) return -1;
-  auto kern = fwd_decode_kernel<T, KV8, NST>;
+  auto kern = fwd_decode_kernel<T, KV8, NST, HD, HDV>;
   const int smem = SM::kBytes + 1024;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return (int)e;
+  static std::atomic<unsigned long long> attr_done{0};   // one bit per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !((attr_done.load(std::memory_order_acquire) >> dev) & 1ull)) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 0 && dev < 64) attr_done.fetch_or(1ull << dev, std::memory_order_release);
+  }
   const int ctas = pl.num_sms * ctas_per_sm(KV8 ? 1 : 2);
   int grid = a.total_work < ctas ? a.total_work : ctas;
   if (grid <= 0) return 0;
@@ -639,26 +660,33 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
 
 }  // namespace dec
 
-// Shapes the decode route takes: head_dim 128, 16-bit queries, K/V contiguous or in pages of 16 or 32 keys or whole
-// 64-key TMA boxes.
+// Shapes the decode route takes: head_dim 64, 128 or 192 (values 128), 16-bit queries, a cache of the same type or
+// (head_dim 128) of e4m3 bytes, K/V contiguous or in pages of 16 or 32 keys or whole 64-key TMA boxes.  These are the
+// head dims of the reference's paged kernel (kernels/fa4_blackwell.cu:9958-9983).
 bool decode_supported(const PlanInput& in) {
   if (in.q_dtype == FA_DT_FP8_E4M3) return false;
   if (in.kv_dtype != in.q_dtype && in.kv_dtype != FA_DT_FP8_E4M3) return false;
-  if (in.hd != 128 || in.hdv != 128) return false;
+  const bool hd_ok = (in.hd == 128 && in.hdv == 128) ||
+                     (in.kv_dtype != FA_DT_FP8_E4M3 && ((in.hd == 64 && in.hdv == 64) || (in.hd == 192 && in.hdv == 128)));
+  if (!hd_ok) return false;
   const int ps = in.page_size;
   if (!(ps == 0 || ps == 16 || ps == 32 || ps % 64 == 0)) return false;   // pages divide a 64-row TMA box or are whole boxes
   return in.hkv > 0 && in.hq % in.hkv == 0 && in.tc_layout_ok;
 }
 
+template <typename T>
+static int launch_decode_t(const KParams& kp, const Plan& pl, int slots, cudaStream_t stream) {
+  if (kp.kv_fp8) return dec::launch_t<T, true, 4, 128, 128>(kp, pl, slots, stream);
+  if (kp.hd == 64) return dec::launch_t<T, false, 10, 64, 64>(kp, pl, slots, stream);
+  if (kp.hd == 192) return dec::launch_t<T, false, 4, 192, 128>(kp, pl, slots, stream);
+  return dec::launch_t<T, false, 5, 128, 128>(kp, pl, slots, stream);
+}
+
 int launch_decode(const KParams& kp, const Plan& pl, int compute_dtype, cudaStream_t stream) {
-  // every (batch, m_tile) slot of the metadata may hold a work entry; m_tile is always 0 on this route
+  // every (batch, m_tile) slot of the metadata may hold a work entry
   const int slots = kp.batch * pl.max_mtiles;
-  const bool bf = compute_dtype != FA_DT_FP16;
-  if (kp.kv_fp8)
-    return bf ? dec::launch_t<__nv_bfloat16, true, 4>(kp, pl, slots, stream)
-              : dec::launch_t<__half, true, 4>(kp, pl, slots, stream);
-  return bf ? dec::launch_t<__nv_bfloat16, false, 5>(kp, pl, slots, stream)
-            : dec::launch_t<__half, false, 5>(kp, pl, slots, stream);
+  return compute_dtype != FA_DT_FP16 ? launch_decode_t<__nv_bfloat16>(kp, pl, slots, stream)
+                                     : launch_decode_t<__half>(kp, pl, slots, stream);
 }
 
 }  // namespace fa

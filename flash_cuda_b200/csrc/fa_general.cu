@@ -42,8 +42,11 @@ __global__ void __launch_bounds__(NTHREADS) fwd_general_kernel(const KParams p) 
   T* sV = sK + BN * LDQ;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int mt = blockIdx.x, hk = blockIdx.y;
-  const int b = blockIdx.z % p.batch, split = blockIdx.z / p.batch;
+  // grid: x = (split * batch + b) * mtiles + m tile (x has the 2^31 range; y and z stop at 65535), y = kv head
+  const int mtiles = (p.max_seqlen_q * p.rep + BM - 1) / BM;
+  const int mt = blockIdx.x % mtiles, hk = blockIdx.y;
+  const int bz = blockIdx.x / mtiles;
+  const int b = bz % p.batch, split = bz / p.batch;
   const int rep = p.rep;
 
   const int q0 = p.cu_q[b];
@@ -253,12 +256,21 @@ __global__ void __launch_bounds__(NTHREADS) fwd_general_kernel(const KParams p) 
         m = mn;
       }
       const float inv = l > 0.f ? osc * vds / l : 0.f;
-      T* op = reinterpret_cast<T*>(p.out) + qi * p.o_row_stride + (int64_t)head * p.o_head_stride;
+      if (p.out_f32) {
+        float* of = reinterpret_cast<float*>(p.out) + qi * p.o_row_stride + (int64_t)head * p.o_head_stride;
 #pragma unroll
-      for (int nt = 0; nt < HDV / 8; ++nt) {
-        const int c = nt * 8 + 2 * (lane & 3);
-        if (c < p.hdv)
-          *reinterpret_cast<uint32_t*>(op + c) = pack2<T>(o[nt][2 * half] * inv, o[nt][2 * half + 1] * inv);
+        for (int nt = 0; nt < HDV / 8; ++nt) {
+          const int c = nt * 8 + 2 * (lane & 3);
+          if (c < p.hdv) *reinterpret_cast<float2*>(of + c) = make_float2(o[nt][2 * half] * inv, o[nt][2 * half + 1] * inv);
+        }
+      } else {
+        T* op = reinterpret_cast<T*>(p.out) + qi * p.o_row_stride + (int64_t)head * p.o_head_stride;
+#pragma unroll
+        for (int nt = 0; nt < HDV / 8; ++nt) {
+          const int c = nt * 8 + 2 * (lane & 3);
+          if (c < p.hdv)
+            *reinterpret_cast<uint32_t*>(op + c) = pack2<T>(o[nt][2 * half] * inv, o[nt][2 * half + 1] * inv);
+        }
       }
       if ((lane & 3) == 0) p.lse[(int64_t)head * p.total_q + qi] = l > 0.f ? (m + lg2(l)) * kLn2 : -INFINITY;
     }
@@ -272,7 +284,8 @@ static int launch_t(const KParams& kp, cudaStream_t stream) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return (int)e;
   const int mtiles = (kp.max_seqlen_q * kp.rep + BM - 1) / BM;
-  dim3 grid(mtiles, kp.hkv, kp.batch * kp.nsplits);
+  if (kp.hkv > 65535 || (long long)mtiles * kp.batch * kp.nsplits > 2147483647ll) return -1;
+  dim3 grid((unsigned)(mtiles * kp.batch * kp.nsplits), kp.hkv, 1);
   kern<<<grid, NTHREADS, smem, stream>>>(kp);
   return (int)cudaGetLastError();
 }

@@ -4,6 +4,7 @@
 #include <stdint.h>
 
 #include "../../include/fa_b200.h"
+#include "fa_sched.h"
 
 namespace fa {
 
@@ -27,8 +28,10 @@ struct KParams {
   const float* k_descale;
   const float* v_descale;
   const float* s_aux;
-  const int32_t* work;      // scheduler metadata / work list (layout in fa_sched.h)
-  int32_t* counters;        // zeroed per call: [0] = persistent work counter
+  const int32_t* work;      // scheduler metadata / work list (layout in fa_sched.h), or null
+  SchedExpect work_expect;  // header values `work` must carry
+  int32_t* counters;        // zero at kernel start: [0] = persistent work counter, [1] = CTAs that have finished;
+                            // the last CTA to finish sets both back to zero
   DeviceStatus* status;
   int64_t q_row_stride, q_head_stride;
   int64_t k_row_stride, k_head_stride, k_page_stride;
@@ -41,6 +44,7 @@ struct KParams {
   int32_t q_fp8, kv_fp8;
   int32_t is_causal, window_left, window_right;
   int32_t nsplits;
+  int32_t out_f32;     // `out` is fp32 (FA_DT_FP32) instead of the 16-bit type of the kernel
   float scale;         // softmax_scale
   float softcap;       // 0 = off
 };

@@ -11,7 +11,12 @@
 //   warps 10-11 idle (they complete the third warpgroup so that register tiers can be set per warpgroup)
 // Work items (256 query rows of one (batch, head); late = heavy tiles first) are handed out through one global
 // atomic counter, so SMs that finish early take more; the TMA lane decodes each item once (sequence bounds,
-// key-block ranges) and publishes it, one item ahead, in a two-slot mailbox in shared memory.
+// key-block ranges) and publishes it, one item ahead, in a two-slot mailbox in shared memory.  The items come
+// either from arithmetic on the work id (slots of a ragged batch that own no query row are skipped by the TMA
+// lane without a hand-off) or, when the call carries scheduler metadata for this route, from that sorted list.
+// Epilogue: a softmax thread pulls its whole O row into registers and releases O at once (the next item's first
+// PV may then overwrite it); where a warp's 32 rows all lie inside the sequence the rows go out through a
+// swizzled 4 KB staging buffer per warp and one TMA store per 64 columns, else through plain stores.
 // TMEM (512 columns): S0 [0,128) S1 [128,256) O0 [256,384) O1 [384,512); P_t overlays the first 64
 // columns of S_t once the owning thread has read its S row.
 // The tensor pipe runs [PV0(i), QK0(i+1), PV1(i), QK1(i+1)] so that one tile's softmax overlaps the other
@@ -25,6 +30,7 @@
 // and head_dim 192/128 in the one kernel.
 #include <cuda.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "fa_internal.h"
@@ -42,10 +48,15 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 enum Role : unsigned { ROLE_TMA = 1, ROLE_MMA = 2, ROLE_SOFTMAX = 3, ROLE_EPILOGUE = 4 };
 
+constexpr int kEndOfWork = 0x7fffffff;
+constexpr int kTwoTermBlocks = 2;   // e4m3: tiles that see at most this many key blocks keep P as two e4m3 terms
+
 struct TcArgs {
   KParams kp;
-  int num_items;     // batch * hq * max_pairs
+  int num_items;     // batch * hq * max_pairs: the work ids of the arithmetic order (an upper bound with a list)
   int max_pairs;
+  int use_list;      // kp.work holds scheduler metadata of this route: items = its valid entries x hq
+  int stage_out;     // map_o is valid: full 32-row groups leave through shared memory and TMA stores
   int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128)
   int kv_total_rows; // rows of the K/V tensor map (out-of-range y => zero fill)
   int out_cols;      // value columns that exist (head_dim 96 runs as 128 with zero-filled columns 96..127)
@@ -64,12 +75,19 @@ template <> struct Elem<fp8_t> {
   using Out = __nv_bfloat16;
 };
 
+constexpr int kSmemLimit = 232448;   // dynamic shared memory one CTA may ask for on sm_100
+
 template <int ESZ, int HD, int HDV, int KST, int VST>
 struct Smem {
   static constexpr int kQBytes = 2 * TM * HD * ESZ;
   static constexpr int kKStage = TN * HD * ESZ;
   static constexpr int kVStage = TN * HDV * ESZ;
-  static constexpr int kBarOff = kQBytes + KST * kKStage + VST * kVStage;
+  static constexpr int kRings = kQBytes + KST * kKStage + VST * kVStage;
+  // output staging: 8 softmax warps x (32 rows x 64 16-bit columns), when it fits beside the rings
+  static constexpr int kStageBytes = 8 * 4096;
+  static constexpr bool kStageOut = kRings + kStageBytes + 3 * 1024 <= kSmemLimit;
+  static constexpr int kStageOff = kRings;
+  static constexpr int kBarOff = kRings + (kStageOut ? kStageBytes : 0);
   static constexpr int kNumBars = 2 + KST + 2 * VST + 8 + 1 + 4 + 1 + KST;
   static constexpr int kItemOff = kBarOff + ((kNumBars * 8 + 16 + 15) & ~15);   // after abort flags and TMEM base
   static constexpr int kBytes = kItemOff + 2 * 64;             // two mailbox slots of one decoded work item each
@@ -82,19 +100,34 @@ struct alignas(16) Item {
   int lo[2], hi[2];   // key-block range per tile
   int ulo, uhi;       // union
   int valid;
-  int w;              // work id; >= num_items ends the role loops
+  int w;              // work id; kEndOfWork ends the role loops
 };
 static_assert(sizeof(Item) == 64, "mailbox slot");
 
-__device__ __forceinline__ Item decode_item(const TcArgs& a, int w) {
+__device__ __forceinline__ Item decode_item(const TcArgs& a, int w, bool* bad_entry) {
   const KParams& p = a.kp;
   Item it;
   it.w = w;
-  const int per_slot = p.batch * p.hq;
-  const int slot = w / per_slot, rem = w - slot * per_slot;
-  it.pair = a.max_pairs - 1 - slot;          // heavy (late) tiles first under causal masking
-  it.b = rem / p.hq;
-  it.h = rem - it.b * p.hq;
+  if (a.use_list) {
+    // entry e of the sorted list = (batch, 256-row tile); all q heads of one entry are consecutive work ids
+    const int e = w / p.hq;
+    it.h = w - e * p.hq;
+    const int32_t* ent = p.work + kSchedHeader + 4 * e;
+    it.b = ent[0];
+    it.pair = ent[1];
+    if ((unsigned)it.b >= (unsigned)p.batch || (unsigned)it.pair >= (unsigned)a.max_pairs) {
+      *bad_entry = true;
+      it.b = it.pair = it.h = it.q0 = it.seqlen_q = it.seqlen_k = it.k0 = it.leftpad = 0;
+      it.lo[0] = it.lo[1] = it.hi[0] = it.hi[1] = it.ulo = it.uhi = it.valid = 0;
+      return it;
+    }
+  } else {
+    const int per_slot = p.batch * p.hq;
+    const int slot = w / per_slot, rem = w - slot * per_slot;
+    it.pair = a.max_pairs - 1 - slot;          // heavy (late) tiles first under causal masking
+    it.b = rem / p.hq;
+    it.h = rem - it.b * p.hq;
+  }
   it.q0 = p.cu_q[it.b];
   it.seqlen_q = p.cu_q[it.b + 1] - it.q0;
   it.k0 = p.page_table ? 0 : p.cu_k[it.b];
@@ -128,28 +161,11 @@ struct Ring {
   }
 };
 
-// Bounded wait that also gives up when another role has raised the abort flag.
-__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  // common case: a few probes (each probe already sleeps in hardware until the phase flips or a short time passes)
-#pragma unroll 1
-  for (int i = 0; i < 256; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  // slow case: keep probing; look at the abort flag and the SM clock only every 64 probes (about 2 s at 2 GHz)
-  const long long t0 = clock64();
-#pragma unroll 1
-  while (true) {
-#pragma unroll 1
-    for (int i = 0; i < 64; ++i)
-      if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > 4000000000ll) return false;
-  }
-}
-
 template <typename T, int HD, int HDV, int KST, int VST>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
-                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+                      const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                      const __grid_constant__ CUtensorMap map_o) {
   constexpr int ESZ = Elem<T>::kSize;          // bytes per Q/K/V element
   constexpr bool F8 = Elem<T>::kF8;
   constexpr int EPB = 128 / ESZ;               // elements per 128-byte swizzle row
@@ -224,20 +240,39 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       Ring<VST> vr;
       bool ok = true;
       uint32_t wcnt = 0;
-      // work items are handed out heaviest first through one global counter; every role of this CTA learns the
-      // id from a two-slot mailbox in shared memory
+      // number of work ids: from the list's header (checked against this call's geometry before anything is
+      // indexed) or the arithmetic count
+      int num_items = a.num_items;
+      if (a.use_list) {
+        if (sched_header_matches(p.work, p.work_expect)) {
+          num_items = p.work[6] * p.hq;
+        } else {
+          report_error(p.status, DEV_ERR_BAD_INDEX, ROLE_TMA);
+          num_items = 0;
+        }
+      }
+      bool first_ticket = true;
+      // work items are handed out heaviest first: a CTA's first id is its block index, later ones come from one
+      // global counter; every role of this CTA learns the item from a two-slot mailbox in shared memory
       auto fetch_and_publish = [&]() -> Item {
         Item it;
-        it.w = 0x7fffffff;
+        it.w = kEndOfWork;
         const uint32_t slot = wcnt & 1;
         if (!wait_or_abort(bar_w_empty + 8 * slot, ((wcnt >> 1) & 1) ^ 1, s_abort)) {
           report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA);
           ok = false;
           return it;
         }
-        const int w = atomicAdd(p.counters, 1);
-        if (w < a.num_items) it = decode_item(a, w);   // sequence bounds are read from global memory once per item
-        else it.w = w;
+        // ids whose (batch, tile) owns no query row (ragged batches) are dropped here, without a hand-off
+        while (true) {
+          const int w = first_ticket ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(p.counters, 1);
+          first_ticket = false;
+          if (w >= num_items) { it.w = kEndOfWork; break; }
+          bool bad = false;
+          it = decode_item(a, w, &bad);   // sequence bounds are read from global memory once per item
+          if (bad) { report_error(p.status, DEV_ERR_BAD_INDEX, ROLE_TMA); num_items = 0; it.w = kEndOfWork; break; }
+          if (it.valid) break;
+        }
         const int4* src = reinterpret_cast<const int4*>(&it);
         int4* dst = reinterpret_cast<int4*>(&s_item[slot]);
 #pragma unroll
@@ -247,11 +282,11 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         return it;
       };
       Item it_next = fetch_and_publish();
-      while (it_next.w < a.num_items && ok) {
+      while (it_next.w != kEndOfWork && ok) {
         const Item it = it_next;
         // the next item is fetched one ahead, but only after this item's first loads are on their way: the
         // counter round trip and the decoding then hide behind them
-        if (!it.valid || it.uhi <= it.ulo) { it_next = fetch_and_publish(); continue; }
+        if (it.uhi <= it.ulo) { it_next = fetch_and_publish(); continue; }   // rows without keys: only an epilogue
         ok = wait_or_abort(bar_q_empty, (qcnt & 1) ^ 1, s_abort);
         if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
         mbar_expect_tx(bar_q_full, SM::kQBytes);
@@ -324,6 +359,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       for (uint32_t s = 0; s < (uint32_t)VST; ++s) {
         if (vr.n > s) { const uint32_t last = (vr.n - 1 - s) / VST; wait_or_abort(bar_v_full + 8 * s, last & 1, s_abort + 1); }
       }
+      counters_release(p.counters);   // this CTA takes no more tickets
     }
   } else if (warp == WARP_MMA) {
     // =========================================== MMA issuer =============================================
@@ -373,13 +409,22 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         umma_commit(bar_s_full + 8 * t);
       }
     };
-    auto issue_pv = [&](int t, uint32_t vslot, bool first) {
+    // two_term (e4m3 only): P was written as P_hi (columns 0..31 of S_t) + P_lo (columns 32..63), see the softmax role
+    auto issue_pv = [&](int t, uint32_t vslot, bool first, bool two_term) {
       const uint64_t vd = vd0 + (uint64_t)(vslot * (SM::kVStage >> 4));
       if (leader) {
 #pragma unroll
         for (int ks = 0; ks < TN / KEL; ++ks)   // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
           umma_ts<F8>(tmem_u + 256 + t * 128, tmem_u + t * TN + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
                       (!first || ks > 0) ? 1u : 0u);
+        if constexpr (F8) {
+          if (two_term) {
+#pragma unroll
+            for (int ks = 0; ks < TN / KEL; ++ks)
+              umma_ts<F8>(tmem_u + 256 + t * 128, tmem_u + t * TN + 32 + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)),
+                          idesc_pv, 1u);
+          }
+        }
       }
     };
     auto commit = [&](uint32_t bar) { if (leader) umma_commit(bar); };
@@ -396,7 +441,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       const int valid = __shfl_sync(FULL, rb.z, 0), w = __shfl_sync(FULL, rb.w, 0);
       if (leader) mbar_arrive(bar_w_empty + 8 * slot);
       ++wcnt;
-      if (__any_sync(FULL, fail) || w >= a.num_items) break;
+      if (__any_sync(FULL, fail) || w == kEndOfWork) break;
       if (!valid || uhi <= ulo) continue;
       const int lo[2] = {lo0, lo1}, hi[2] = {hi0, hi1};
       wait(bar_q_full, qcnt & 1);
@@ -430,7 +475,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
             }
             wait(bar_p_full + 8 * t, pcnt[t] & 1);
             tc_fence_after_sync();
-            issue_pv(t, vs, first);
+            issue_pv(t, vs, first, F8 && hi[t] - lo[t] <= kTwoTermBlocks);
             ++pcnt[t];
             if (i + 1 == hi[t]) commit(bar_o_full + 8 * t);
           }
@@ -469,7 +514,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     uint32_t wcnt = 0;
     auto next_work = [&]() -> Item {
       Item it;
-      it.w = 0x7fffffff;
+      it.w = kEndOfWork;
       const uint32_t slot = wcnt & 1;
       if (!wait_or_abort(bar_w_full + 8 * slot, (wcnt >> 1) & 1, s_abort)) { ok = false; return it; }
       const int4* src = reinterpret_cast<const int4*>(&s_item[slot]);
@@ -481,7 +526,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       ++wcnt;
       return it;
     };
-    for (Item it = next_work(); it.w < a.num_items && ok; it = next_work()) {
+    for (Item it = next_work(); it.w != kEndOfWork && ok; it = next_work()) {
       if (!it.valid) continue;
       const int row0 = it.pair * 2 * TM + t * TM;
       if (row0 >= it.seqlen_q) continue;           // this tile owns no row
@@ -508,6 +553,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       if (p.window_right >= 0) hi_min = min(hi_min, qp_first + p.window_right);
       if (p.window_left >= 0) lo_max = max(lo_max, qp_last - p.window_left);
 
+      const bool two_term = F8 && (it.hi[t] - it.lo[t] <= kTwoTermBlocks);   // tile-uniform; see the P store below
       float m_used = -INFINITY, l = 0.f;
       float lr = 0.f;   // e4m3 only: sum of the ROUNDED probabilities (normalises O); l stays exact for the LSE
       for (int i = it.lo[t]; i < it.hi[t]; ++i) {
@@ -555,11 +601,17 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         const float y_max = mx * c_mul;               // c_mul > 0, so the maximum commutes with the scale
         float corr = 1.f;
         bool rescale = false;
+        // m_used is the reference point of the exponentials, p = 2^(y - m_used).  For 16-bit P it is the row
+        // maximum when it was last taken, so p <= 2^8 between rescales.  e4m3 P has few exponent values below 1
+        // (normal down to 2^-6), so there the reference sits 2^5 BELOW the maximum: p runs up to 2^5..2^8 <= 448
+        // and probabilities down to 2^-11 of the maximum keep their three mantissa bits.  Numerator and
+        // denominator carry the same factor; the LSE is taken from the reference point and the sum as they are.
+        constexpr float kRefShift = F8 ? 5.f : 0.f;
         if (m_used == -INFINITY) {
-          m_used = y_max;                             // first block with a visible key (may stay -inf)
+          m_used = y_max - kRefShift;                 // first block with a visible key (may stay -inf)
         } else if (y_max > m_used + kRescaleThreshold) {
-          corr = ex2(m_used - y_max);
-          m_used = y_max;
+          corr = ex2(m_used - (y_max - kRefShift));
+          m_used = y_max - kRefShift;
           l *= corr;
           lr *= corr;
           rescale = true;
@@ -596,7 +648,10 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
             } else {
               // four e4m3 probabilities per TMEM column.  The row sum is taken over the ROUNDED probabilities, so
               // that numerator (P V on the tensor cores) and denominator describe the same weights.
-              uint32_t pk[8];
+              // A tile whose rows see at most kTwoTermBlocks key blocks in all (256 keys: the first rows of a causal
+              // sequence, short sequences) has little averaging over keys to hide the 3-bit mantissa of P: there P is
+              // written as two e4m3 terms, P_hi + P_lo with P_lo = round(P - P_hi), and the MMA warp runs PV over both.
+              uint32_t pk[8], pl[8];
               __half2 hs[4] = {__half2(), __half2(), __half2(), __half2()};
 #pragma unroll
               for (int j = 0; j < 32; j += 4) {
@@ -607,10 +662,19 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
                 const uint32_t q4 = pack4_e4m3(p0.x, p0.y, p1.x, p1.y);
                 pk[j >> 2] = q4;
                 const uint32_t h0 = e4m3x2_to_f16x2((uint16_t)(q4 & 0xffffu)), h1 = e4m3x2_to_f16x2((uint16_t)(q4 >> 16));
-                hs[(j >> 2) & 3] = __hadd2(hs[(j >> 2) & 3],
-                                           __hadd2(*reinterpret_cast<const __half2*>(&h0), *reinterpret_cast<const __half2*>(&h1)));
+                __half2 hsum = __hadd2(*reinterpret_cast<const __half2*>(&h0), *reinterpret_cast<const __half2*>(&h1));
+                if (two_term) {
+                  const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h0));
+                  const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h1));
+                  const uint32_t r4 = pack4_e4m3(p0.x - f0.x, p0.y - f0.y, p1.x - f1.x, p1.y - f1.y);
+                  pl[j >> 2] = r4;
+                  const uint32_t g0 = e4m3x2_to_f16x2((uint16_t)(r4 & 0xffffu)), g1 = e4m3x2_to_f16x2((uint16_t)(r4 >> 16));
+                  hsum = __hadd2(hsum, __hadd2(*reinterpret_cast<const __half2*>(&g0), *reinterpret_cast<const __half2*>(&g1)));
+                }
+                hs[(j >> 2) & 3] = __hadd2(hs[(j >> 2) & 3], hsum);
               }
               tmem_st8(tS + c * 8, pk);
+              if (two_term) tmem_st8(tS + 32 + c * 8, pl);
               const float2 f01 = __half22float2(__hadd2(hs[0], hs[1])), f23 = __half22float2(__hadd2(hs[2], hs[3]));
               lr += (f01.x + f23.x) + (f01.y + f23.y);
             }
@@ -629,12 +693,26 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       if (!ok) break;
 
       // ---- epilogue of this tile ----
+      // The whole O row goes to registers first and O_t is released at once: the MMA warp may start the next
+      // item's first PV while this thread is still normalising and storing.
       const bool had_blocks = it.hi[t] > it.lo[t];
+      uint32_t o[HDV / 32][32];
       if (had_blocks) {
         ok = wait_or_abort(bar_o_full + 8 * t, ocnt & 1, s_abort);
         ++ocnt;
         if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_EPILOGUE); break; }
         tc_fence_after_sync();
+#pragma unroll
+        for (int c = 0; c < HDV / 32; ++c) tmem_ld32(tO + c * 32, o[c]);
+        tmem_wait_ld();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_o_empty + 8 * t);
+      } else {
+#pragma unroll
+        for (int c = 0; c < HDV / 32; ++c)
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[c][j] = 0u;
       }
       float m_fin = m_used, l_fin = l, osc = 1.f;
       float l_norm = F8 ? lr : l;          // what O is divided by
@@ -648,37 +726,76 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         m_fin = mn;
       }
       const float inv = l_norm > 0.f ? osc * vds / l_norm : 0.f;
+      const float2 inv2 = make_float2(inv, inv);
       const bool row_ok = row < it.seqlen_q;
-      TO* op = reinterpret_cast<TO*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
-#pragma unroll 1
-      for (int c = 0; c < a.out_cols / 32; ++c) {
-        uint32_t o[32];
-        if (had_blocks) {
-          tmem_ld32(tO + c * 32, o);
-          tmem_wait_ld();
-        } else {
+      const int wrow0 = row0 + (warp & 3) * 32;            // first row of this warp's 32
+      bool staged = false;
+      if constexpr (SM::kStageOut) staged = a.stage_out && (wrow0 + 32 <= it.seqlen_q);   // warp-uniform
+      if (staged) {
+        if constexpr (SM::kStageOut) {
+          const uint32_t stg = base + SM::kStageOff + (uint32_t)warp * 4096u;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) o[j] = 0u;
+          for (int hf = 0; hf < HDV / 64; ++hf) {
+            uint32_t pk[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float2 v = fmul2(make_float2(__uint_as_float(o[2 * hf + (j >> 4)][(2 * j) & 31]),
+                                                 __uint_as_float(o[2 * hf + (j >> 4)][((2 * j) & 31) + 1])), inv2);
+              pk[j] = pack2<TO>(v.x, v.y);
+            }
+            // the store issued for the previous 64 columns (or the previous item) must have read the buffer
+            if (lane == 0) bulk_wait_read_all();
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {   // 16-byte chunk c of row `lane`, at its 128-byte-swizzle position
+              const uint32_t addr = stg + (uint32_t)lane * 128u + ((uint32_t)(c ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
+                           "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&map_o, stg, hf * 64, it.h, it.q0 + wrow0);
+              bulk_commit_group();
+            }
+          }
         }
-        if (row_ok) {
+      } else if (row_ok) {
+        if (p.out_f32) {
+          float* op = reinterpret_cast<float*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 v;
-            v.x = pack2<TO>(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
-            v.y = pack2<TO>(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
-            v.z = pack2<TO>(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
-            v.w = pack2<TO>(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
-            *reinterpret_cast<uint4*>(op + c * 32 + j) = v;
+          for (int c = 0; c < HDV / 32; ++c) {
+            if (c * 32 < a.out_cols) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(op + c * 32 + j) =
+                    make_float4(__uint_as_float(o[c][j]) * inv, __uint_as_float(o[c][j + 1]) * inv,
+                                __uint_as_float(o[c][j + 2]) * inv, __uint_as_float(o[c][j + 3]) * inv);
+            }
+          }
+        } else {
+          TO* op = reinterpret_cast<TO*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
+#pragma unroll
+          for (int c = 0; c < HDV / 32; ++c) {
+            if (c * 32 < a.out_cols) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 v;
+                v.x = pack2<TO>(__uint_as_float(o[c][j]) * inv, __uint_as_float(o[c][j + 1]) * inv);
+                v.y = pack2<TO>(__uint_as_float(o[c][j + 2]) * inv, __uint_as_float(o[c][j + 3]) * inv);
+                v.z = pack2<TO>(__uint_as_float(o[c][j + 4]) * inv, __uint_as_float(o[c][j + 5]) * inv);
+                v.w = pack2<TO>(__uint_as_float(o[c][j + 6]) * inv, __uint_as_float(o[c][j + 7]) * inv);
+                *reinterpret_cast<uint4*>(op + c * 32 + j) = v;
+              }
+            }
           }
         }
       }
-      if (had_blocks) {
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_o_empty + 8 * t);
-      }
       if (row_ok)
         p.lse[(int64_t)it.h * p.total_q + it.q0 + row] = l_fin > 0.f ? (m_fin + lg2(l_fin)) * kLn2 : -INFINITY;
+    }
+    if constexpr (SM::kStageOut) {
+      if (lane == 0) bulk_wait_all();   // this lane's output stores have completed before the CTA leaves
     }
     if (!ok) *s_abort = 1;
   }
@@ -710,8 +827,32 @@ static EncodeTiledFn get_encode_fn() {
 
 // 3-D map over [rows][heads][head_dim] (innermost first: column, head, row); box = 128 bytes of one head x box_rows
 // rows.  Columns of a box past head_dim are filled with zeros, which is how head_dim 96 rides on the 128-wide kernel.
+// Encoding is pure host arithmetic on its arguments, so the last few results are kept per thread: a serving loop
+// that calls with the same tensors again (the KV pool, a reused Q/O buffer) skips the driver call.
+struct MapKey {
+  const void* ptr;
+  uint64_t rows, heads, head_dim, head_stride, row_stride;
+  uint32_t box_rows;
+  int dtype;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && heads == o.heads && head_dim == o.head_dim && head_stride == o.head_stride &&
+           row_stride == o.row_stride && box_rows == o.box_rows && dtype == o.dtype;
+  }
+};
+struct MapCache {
+  static constexpr int N = 16;
+  MapKey key[N];
+  CUtensorMap map[N];
+  bool used[N] = {};
+  int next = 0;
+};
+
 static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t rows, uint64_t heads, uint64_t head_dim,
                         uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_rows) {
+  static thread_local MapCache cache;
+  const MapKey k{ptr, rows, heads, head_dim, head_stride_elems, row_stride_elems, box_rows, dtype};
+  for (int i = 0; i < MapCache::N; ++i)
+    if (cache.used[i] && cache.key[i] == k) { *m = cache.map[i]; return true; }
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   const uint32_t esz = dtype == FA_DT_FP8_E4M3 ? 1 : 2;
@@ -722,9 +863,16 @@ static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t row
   const CUtensorMapDataType dt = dtype == FA_DT_FP8_E4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : dtype == FA_DT_FP16   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  return fn(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (fn(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  const int slot = cache.next;
+  cache.next = (cache.next + 1) % MapCache::N;
+  cache.key[slot] = k;
+  cache.map[slot] = *m;
+  cache.used[slot] = true;
+  return true;
 }
 
 template <typename T, int HD, int HDV, int KST, int VST>
@@ -734,22 +882,39 @@ static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
   a.kp = kp;
   a.max_pairs = (kp.max_seqlen_q + 2 * TM - 1) / (2 * TM);
   a.num_items = kp.batch * kp.hq * a.max_pairs;
+  a.use_list = kp.work != nullptr;
   const bool paged = kp.page_table != nullptr;
   a.kv_box_rows = paged ? (kp.page_size < TN ? kp.page_size : TN) : TN;
   a.kv_total_rows = (int)kv_rows;
   a.out_cols = kp.hdv;
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   if (!make_map_3d(&mq, kp.q, dtype, (uint64_t)kp.total_q, kp.hq, kp.hd, kp.hd, (uint64_t)kp.q_row_stride, TM)) return -1;
   if (!make_map_3d(&mk, kp.k, dtype, kv_rows, kp.hkv, kp.hd, kp.hd, (uint64_t)kp.k_row_stride, a.kv_box_rows)) return -1;
   if (!make_map_3d(&mv, kp.v, dtype, kv_rows, kp.hkv, kp.hdv, kp.hdv, (uint64_t)kp.v_row_stride, a.kv_box_rows)) return -1;
+  // output map (16-bit element type of the output): 64 columns x 32 rows per store.  A layout TMA cannot describe
+  // only switches the staged path off.
+  a.stage_out = 0;
+  mo = mq;
+  if (SM::kStageOut && !kp.out_f32) {
+    const int odt = dtype == FA_DT_FP16 ? FA_DT_FP16 : FA_DT_BF16;
+    if (make_map_3d(&mo, kp.out, odt, (uint64_t)kp.total_q, kp.hq, kp.hdv, (uint64_t)kp.o_head_stride,
+                    (uint64_t)kp.o_row_stride, 32))
+      a.stage_out = 1;
+  }
   auto kern = fwd_prefill_tc_kernel<T, HD, HDV, KST, VST>;
   int smem = SM::kBytes + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;   // one CTA per SM: the CTA owns all 512 TMEM columns
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-  if (e != cudaSuccess) return (int)e;
+  static std::atomic<unsigned long long> attr_done{0};   // one bit per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !((attr_done.load(std::memory_order_acquire) >> dev) & 1ull)) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 0 && dev < 64) attr_done.fetch_or(1ull << dev, std::memory_order_release);
+  }
   const int grid = a.num_items < pl.num_sms ? a.num_items : pl.num_sms;
   if (grid <= 0) return 0;
-  kern<<<grid, NTHREADS, smem, stream>>>(a, mq, mk, mv);
+  kern<<<grid, NTHREADS, smem, stream>>>(a, mq, mk, mv, mo);
   return (int)cudaGetLastError();
 }
 

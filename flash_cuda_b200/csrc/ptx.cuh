@@ -55,14 +55,39 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait. Returns false after ~`limit` failed probes (each probe itself blocks for a
-// hardware-defined slice), so a protocol bug ends the kernel instead of hanging the GPU.
-constexpr uint32_t kWaitLimit = 4u << 20;
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit = kWaitLimit) {
-  for (uint32_t i = 0; i < limit; ++i) {
+// Bounded wait that also gives up when another role has raised the abort flag.  Returns false when the phase
+// did not complete within `budget_cycles` of the SM clock (default: about 2 s at 2 GHz), so a protocol bug or a
+// lost arrival ends the kernel with an error code instead of hanging the GPU.
+constexpr long long kWaitBudgetCycles = 4000000000ll;
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                              long long budget_cycles = kWaitBudgetCycles) {
+  // common case: a few probes (each probe already sleeps in hardware until the phase flips or a short time passes)
+#pragma unroll 1
+  for (int i = 0; i < 256; ++i)
     if (mbar_try_wait(bar, parity)) return true;
+  // slow case: keep probing; look at the abort flag and the SM clock only every 64 probes
+  const long long t0 = clock64();
+#pragma unroll 1
+  while (true) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > budget_cycles) return false;
   }
-  return false;
+}
+
+// Persistent kernels take work ids from counters[0].  ONE thread of every CTA calls this after the CTA's last
+// ticket: the last CTA of the grid to arrive puts both words back to zero, so the next launch on the stream
+// finds them clean without a memset in between.
+__device__ __forceinline__ void counters_release(int32_t* counters) {
+  __threadfence();
+  const int done = atomicAdd(&counters[1], 1);
+  if (done == (int)(gridDim.x * gridDim.y * gridDim.z) - 1) {
+    counters[0] = 0;
+    counters[1] = 0;
+    __threadfence();
+  }
 }
 
 // One lane of the (fully converged) warp, the same lane every time: gates instructions that ONE thread must issue
@@ -109,6 +134,19 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, int x
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
+
+// 3-D tiled store shared -> global (bulk async group of the issuing thread).  x * elem_size must be a multiple of
+// 16 bytes and no coordinate may be negative; elements outside the tensor are not written.
+__device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int x, int y, int z) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+               ::"l"(map), "r"(x), "r"(y), "r"(z), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the issuing thread's earlier bulk stores have finished READING shared memory (the buffer may be rewritten)
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... have completed altogether
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // ----------------------------------------------------------------------------------------------
 // tcgen05: tensor memory + MMA
@@ -299,6 +337,15 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
   asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  unsigned long long ra, rb, rd;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
   float2 d;
   asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
   return d;

@@ -9,7 +9,9 @@
 #include <torch/library.h>
 
 #include <cstdlib>
+#include <mutex>
 #include <optional>
+#include <unordered_map>
 #include <vector>
 
 #include "../../include/fa_b200.h"
@@ -34,9 +36,59 @@ const int32_t* i32(const std::optional<at::Tensor>& t, const char* name) {
   return t->data_ptr<int32_t>();
 }
 
-bool env_flag(const char* name) {
-  const char* v = std::getenv(name);
-  return v && v[0] && v[0] != '0';
+// Environment switches, read once when the library is loaded:
+//   FA_B200_ROUTE=<0..3>        force a kernel family (FA_ROUTE_*), for testing and A/B runs
+//   FA_B200_CHECK_STATUS=1      synchronise after every call and read the device status word
+struct EnvConfig {
+  int route = FA_ROUTE_AUTO;
+  bool check_status = false;
+  EnvConfig() {
+    if (const char* r = std::getenv("FA_B200_ROUTE")) route = std::atoi(r);
+    const char* v = std::getenv("FA_B200_CHECK_STATUS");
+    check_status = v && v[0] && v[0] != '0';
+  }
+};
+const EnvConfig& env_config() {
+  static const EnvConfig cfg;
+  return cfg;
+}
+
+// Scratch for fa_b200_fwd, kept per (device, stream) and reused: its 256-byte header is zeroed once when the
+// buffer is made and every call leaves it zero again (FA_FLAG_WORKSPACE_CLEAN), so a call costs neither an
+// allocation nor a memset.  Calls on one stream run one after the other, which is what sharing a buffer needs.
+// Requests above kCacheLimit are served by a plain allocation instead.
+constexpr int64_t kCacheLimit = 64ll << 20;
+struct WsKey {
+  int device;
+  cudaStream_t stream;
+  bool operator==(const WsKey& o) const { return device == o.device && stream == o.stream; }
+};
+struct WsKeyHash {
+  size_t operator()(const WsKey& k) const { return std::hash<const void*>()(k.stream) * 31u + (size_t)k.device; }
+};
+std::mutex g_ws_mu;
+std::unordered_map<WsKey, at::Tensor, WsKeyHash> g_ws_cache;
+
+at::Tensor cached_workspace(const at::Tensor& like, cudaStream_t stream, int64_t bytes, bool* clean) {
+  if (bytes > kCacheLimit) {
+    *clean = false;
+    return at::empty({bytes}, like.options().dtype(at::kByte));
+  }
+  const WsKey key{(int)like.get_device(), stream};
+  std::lock_guard<std::mutex> lk(g_ws_mu);
+  auto it = g_ws_cache.find(key);
+  if (it == g_ws_cache.end() || it->second.numel() < bytes) {
+    const int64_t cap = std::max<int64_t>(bytes, 1 << 20);
+    at::Tensor t = at::zeros({cap}, like.options().dtype(at::kByte));   // zero-filled on the current stream
+    if (it == g_ws_cache.end()) it = g_ws_cache.emplace(key, t).first;
+    else it->second = t;
+  }
+  *clean = true;
+  return it->second;
+}
+void drop_cached_workspace(const at::Tensor& like, cudaStream_t stream) {
+  std::lock_guard<std::mutex> lk(g_ws_mu);
+  g_ws_cache.erase(WsKey{(int)like.get_device(), stream});
 }
 
 void check_rc(int rc, const char* what) {
@@ -68,15 +120,17 @@ std::vector<at::Tensor> mha_fwd(
     std::optional<at::Tensor> cp_tot_seqused_k) {
   TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "fa_b200: q, k, v must be CUDA tensors");
   const at::cuda::OptionalCUDAGuard guard(q.device());
-  TORCH_CHECK(q.dim() == 3, "fa_b200: q must be (total_q, hq, hd)");
+  TORCH_CHECK(q.dim() == 3, "fa_b200: unsupported config (q must be (total_q, hq, hd))");
   const bool paged = page_table.has_value();
-  TORCH_CHECK(k.dim() == (paged ? 4 : 3) && v.dim() == k.dim(), "fa_b200: k/v rank does not match paged=", paged);
+  TORCH_CHECK(k.dim() == (paged ? 4 : 3) && v.dim() == k.dim(),
+              "fa_b200: unsupported config (k/v rank does not match paged=", paged, ")");
   TORCH_CHECK(!k_new.has_value() && !v_new.has_value() && !q_v.has_value() && !rotary_cos.has_value() &&
                   !rotary_sin.has_value() && !kv_batch_idx.has_value() && !seqused_q.has_value() &&
                   !cu_seqlens_k_new.has_value() && cp_world_size <= 1,
               "fa_b200: unsupported config (k_new/v_new/q_v/rotary/kv_batch_idx/seqused_q/context-parallel)");
   TORCH_CHECK(cu_seqlens_q.has_value(), "fa_b200: unsupported config (cu_seqlens_q is required)");
-  TORCH_CHECK(q.stride(2) == 1 && k.stride(-1) == 1 && v.stride(-1) == 1, "fa_b200: last dim must be contiguous");
+  TORCH_CHECK(q.stride(2) == 1 && k.stride(-1) == 1 && v.stride(-1) == 1,
+              "fa_b200: unsupported config (the last dim of q, k, v must be contiguous)");
 
   FaFwdParams p{};
   p.total_q = (int)q.size(0); p.hq = (int)q.size(1); p.hd = (int)q.size(2);
@@ -86,13 +140,16 @@ std::vector<at::Tensor> mha_fwd(
   p.kv_dtype = dtype_code(k.scalar_type());
   TORCH_CHECK(p.q_dtype >= 0 && p.kv_dtype >= 0 && k.scalar_type() == v.scalar_type(),
               "fa_b200: unsupported config (dtype q=", q.scalar_type(), " k=", k.scalar_type(), ")");
-  const auto out_type = q.scalar_type() == at::kFloat8_e4m3fn ? at::kBFloat16 : q.scalar_type();
-  p.out_dtype = dtype_code(out_type);
+  // `out` is q's type (bf16 for e4m3 q); a caller-supplied float32 `out` asks for the normalised result in fp32,
+  // the form a partial result has before a merge
+  auto out_type = q.scalar_type() == at::kFloat8_e4m3fn ? at::kBFloat16 : q.scalar_type();
+  if (out_.has_value() && out_->scalar_type() == at::kFloat) out_type = at::kFloat;
+  p.out_dtype = out_type == at::kFloat ? FA_DT_FP32 : dtype_code(out_type);
 
   at::Tensor out = out_.has_value() ? *out_ : at::empty({p.total_q, p.hq, p.hdv}, q.options().dtype(out_type));
   TORCH_CHECK(out.scalar_type() == out_type && out.dim() == 3 && out.size(0) == p.total_q && out.size(1) == p.hq &&
                   out.size(2) == p.hdv && out.stride(2) == 1,
-              "fa_b200: out has the wrong shape, dtype or layout");
+              "fa_b200: unsupported config (out has the wrong shape, dtype or layout)");
   at::Tensor lse = at::empty({p.hq, p.total_q}, q.options().dtype(at::kFloat));
 
   p.q = q.data_ptr(); p.k = k.data_ptr(); p.v = v.data_ptr(); p.out = out.data_ptr();
@@ -118,9 +175,13 @@ std::vector<at::Tensor> mha_fwd(
   p.seqused_k = i32(seqused_k, "seqused_k");
   p.leftpad_k = i32(leftpad_k, "leftpad_k");
   p.batch = (int)cu_seqlens_q->numel() - 1;
-  TORCH_CHECK(max_seqlen_q.has_value() && max_seqlen_k.has_value(),
-              "fa_b200: max_seqlen_q and max_seqlen_k are required");
-  p.max_seqlen_q = (int)*max_seqlen_q; p.max_seqlen_k = (int)*max_seqlen_k;
+  // The two maxima are optional in the schema (the reference derives them when absent, through a device-to-host
+  // copy of cu_seqlens, kernels/fa4_blackwell.cu:9427-9431).  Any upper bound serves: the kernels read the true lengths on
+  // the device, so the bounds come from the tensor shapes, without a device-to-host copy.
+  p.max_seqlen_q = max_seqlen_q.has_value() ? (int)*max_seqlen_q : p.total_q;
+  p.max_seqlen_k = max_seqlen_k.has_value() ? (int)*max_seqlen_k
+                   : paged               ? (int)(page_table->size(1) * k.size(1))
+                                         : (int)k.size(0);
 
   // fp8 descales: (batch, hkv) float tables or one-element tensors, materialised as (batch, hkv) fp32
   at::Tensor qd, kd, vd;
@@ -145,28 +206,35 @@ std::vector<at::Tensor> mha_fwd(
     TORCH_CHECK(s_aux_f.numel() == p.hq, "fa_b200: s_aux must have one logit per q head");
     p.s_aux = s_aux_f.data_ptr<float>();
   }
+  // A tensor shorter than the header is a placeholder (the reference's op returns zeros({1}),
+  // kernels/fa4_blackwell.cu:10182) and is ignored; anything longer must be this library's metadata for this very
+  // problem: the length is checked on the host, the header on the device.
   p.scheduler_metadata = i32(scheduler_metadata, "scheduler_metadata");
   if (scheduler_metadata.has_value() && scheduler_metadata->numel() < 16) p.scheduler_metadata = nullptr;
+  if (p.scheduler_metadata) p.scheduler_metadata_len = (int)scheduler_metadata->numel();
 
   p.softmax_scale = (float)softmax_scale; p.softcap = (float)softcap;
   p.is_causal = is_causal ? 1 : 0;
   p.window_left = (int)window_size_left; p.window_right = (int)window_size_right;
   p.num_splits = (int)num_splits; p.sm_margin = (int)sm_margin;
-  p.route = FA_ROUTE_AUTO;
-  if (const char* r = std::getenv("FA_B200_ROUTE")) p.route = std::atoi(r);
+  const EnvConfig& env = env_config();
+  p.route = env.route;
 
   const size_t ws_bytes = fa_b200_fwd_workspace_bytes(&p);
-  at::Tensor ws = at::empty({(int64_t)ws_bytes}, q.options().dtype(at::kByte));
   auto stream = at::cuda::getCurrentCUDAStream();
-  const int rc = fa_b200_fwd(&p, ws.data_ptr(), ws_bytes, (fa_stream_t)stream.stream());
+  bool clean = false;
+  at::Tensor ws = cached_workspace(q, stream.stream(), (int64_t)ws_bytes, &clean);
+  if (clean) p.flags |= FA_FLAG_WORKSPACE_CLEAN;
+  const int rc = fa_b200_fwd(&p, ws.data_ptr(), (size_t)ws.numel(), (fa_stream_t)stream.stream());
   if (rc == FA_ERR_UNSUPPORTED) {
     TORCH_CHECK(false, "fa_b200: unsupported config (hd=", p.hd, " hdv=", p.hdv, " paged=", paged,
                 " page_size=", p.page_size, " q dtype=", q.scalar_type(), " kv dtype=", k.scalar_type(), ")");
   }
   check_rc(rc, "fwd");
-  if (env_flag("FA_B200_CHECK_STATUS")) {
+  if (env.check_status) {
     uint32_t detail = 0;
     const int st = fa_b200_check_status(ws.data_ptr(), (fa_stream_t)stream.stream(), &detail);
+    if (st != FA_OK) drop_cached_workspace(q, stream.stream());   // its header is no longer clean
     TORCH_CHECK(st == FA_OK, "fa_b200: ", fa_b200_strerror(st), " (detail=", detail, ")");
   }
   at::Tensor empty = at::empty({0}, q.options().dtype(at::kFloat));

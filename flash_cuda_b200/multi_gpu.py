@@ -7,15 +7,20 @@
    (kernels/fa4_blackwell.cu:6947: one tile per (batch, head)).
 
 2. `fwd_kv_sharded` — long context: the key range is split evenly, rank r holds keys
-   [r*K/N, (r+1)*K/N) of every sequence as its own paged pool; the queries are replicated.  Each rank
-   computes a normalised partial O_r and LSE_r with the single-GPU op, ONE all-gather brings all partials
-   into local memory, and the split-KV merge kernel (the maths of kernels/fa4_blackwell.cu:5964-5985)
-   produces the result on every rank.  Causal masking is bottom-right aligned on the GLOBAL key count: every
-   rank but the last sees only keys in the past of all queries (requires q_len <= K/N), the last rank is
-   causal on its local length.
+   [r*K/N, (r+1)*K/N) of every sequence as its own paged pool; the queries are replicated.  Each rank's
+   attention kernel writes its normalised partial O_r (fp32) and LSE_r straight into one packed send buffer
+   [O_r | LSE_r]; ONE all-gather brings all partials into local memory, and the split-KV merge kernel (the maths
+   of kernels/fa4_blackwell.cu:5964-5985) reads the gathered buffer in place and produces the result on every
+   rank.  No staging copy sits between kernel, collective and merge.
+   `merge="all_to_all"` is the variant for large rank counts: the partials are exchanged so that rank j receives
+   only query rows [j*T/N, (j+1)*T/N) of every partial (1/N of the all-gather's bytes), merges that slice, and an
+   all-gather of the 16-bit result rows (and of the LSE) completes the output.
+   Causal masking is bottom-right aligned on the GLOBAL key count: every rank but the last sees only keys in the
+   past of all queries (requires q_len <= K/N), the last rank is causal on its local length.
 
-The compute callables are injectable so that the host logic (partitioning, gather order, merge) can be tested
-with gloo on CPU ranks; by default they are the CUDA ops and nothing else is ever substituted.
+The compute callables are injectable so that the host logic (partitioning, buffer layout, collectives, merge) can
+be tested with gloo on CPU ranks; by default they are the CUDA library's entry points and nothing else is ever
+substituted.
 """
 from __future__ import annotations
 
@@ -23,6 +28,8 @@ from typing import Callable, Optional, Tuple
 
 import torch
 import torch.distributed as dist
+
+from . import capi
 
 
 def head_slice(hq: int, hkv: int, rank: int, world: int) -> Tuple[slice, slice]:
@@ -39,9 +46,14 @@ def _default_attn():
     return ops.call_fwd
 
 
-def _default_combine():
-    from . import capi
-    return capi.combine
+def _default_partial(q, k, v, *, out, lse, **kw):
+    """The attention kernel writing an fp32 partial: `out` (total_q, hq, hdv) fp32 and `lse` (hq, total_q) are views
+    into the caller's send buffer."""
+    capi.fwd(q, k, v, out=out, lse=lse, **kw)
+
+
+def _default_combine(o_part, lse_part, s_aux, out_dtype):
+    return capi.combine(o_part, lse_part, s_aux, out_dtype)
 
 
 def fwd_head_sharded(q, k, v, *, rank: int, world: int, attn_fn: Optional[Callable] = None, s_aux=None,
@@ -67,31 +79,74 @@ def fwd_head_sharded(q, k, v, *, rank: int, world: int, attn_fn: Optional[Callab
 
 def fwd_kv_sharded(q, k_local, v_local, *, page_table_local, seqused_k_local, cu_seqlens_q, max_seqlen_q: int,
                    max_seqlen_k_local: int, softmax_scale: float, causal: bool, rank: int, world: int,
-                   group=None, attn_fn: Optional[Callable] = None, combine_fn: Optional[Callable] = None,
-                   s_aux=None, **kw):
+                   group=None, partial_fn: Optional[Callable] = None, combine_fn: Optional[Callable] = None,
+                   attn_fn: Optional[Callable] = None, s_aux=None, merge: str = "all_gather",
+                   out_dtype: Optional[torch.dtype] = None, marks: Optional[list] = None, **kw):
     """Long-context attention with the key range sharded over `world` ranks (see module docstring).
-    Returns (out (total_q, hq, hdv), lse (hq, total_q)) on every rank."""
-    attn_fn = attn_fn or _default_attn()
-    combine_fn = combine_fn or _default_combine()
+    Returns (out (total_q, hq, hdv), lse (hq, total_q)) on every rank.
+
+    `marks`, when given, is a list that receives two CUDA events recorded on the current stream: one after the
+    attention kernel, one after the merge (what lies between them is the collective plus the merge kernel)."""
+    partial_fn = partial_fn or _default_partial
+    combine_fn = combine_fn or _default_combine
     if causal and world > 1 and max_seqlen_q > max_seqlen_k_local:
         raise ValueError("kv sharding needs q_len <= keys per rank so that only the last rank is causal")
     local_causal = causal and rank == world - 1
-    # the sink joins exactly once, in the merge
-    out_r, lse_r = attn_fn(q, k_local, v_local, cu_seqlens_q=cu_seqlens_q, seqused_k=seqused_k_local,
-                           page_table=page_table_local, max_seqlen_q=max_seqlen_q,
-                           max_seqlen_k=max_seqlen_k_local, softmax_scale=softmax_scale, causal=local_causal,
-                           s_aux=s_aux if world == 1 else None, **kw)
+    out_dtype = out_dtype or (torch.bfloat16 if q.dtype == torch.float8_e4m3fn else q.dtype)
+
+    def mark():
+        if marks is not None and q.is_cuda:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            marks.append(ev)
+
+    common = dict(cu_seqlens_q=cu_seqlens_q, seqused_k=seqused_k_local, page_table=page_table_local,
+                  max_seqlen_q=max_seqlen_q, max_seqlen_k=max_seqlen_k_local, softmax_scale=softmax_scale,
+                  causal=local_causal, **kw)
     if world == 1:
-        return out_r, lse_r
-    total_q, hq, hdv = out_r.shape
-    # one packed buffer per rank: [O_r as fp32 | LSE_r], gathered with a single collective
-    packed = torch.empty(total_q * hq * hdv + hq * total_q, device=out_r.device, dtype=torch.float32)
-    packed[:total_q * hq * hdv].view(total_q, hq, hdv).copy_(out_r)
-    packed[total_q * hq * hdv:].view(hq, total_q).copy_(lse_r)
-    gathered = torch.empty(world * packed.numel(), device=out_r.device, dtype=torch.float32)
-    dist.all_gather_into_tensor(gathered, packed, group=group)
-    g = gathered.view(world, packed.numel())
-    # the merge kernel wants (S, total_q, hq, hdv) and (S, hq, total_q), each contiguous
-    o_part = g[:, :total_q * hq * hdv].reshape(world, total_q, hq, hdv).contiguous()
-    lse_part = g[:, total_q * hq * hdv:].reshape(world, hq, total_q).contiguous()
-    return combine_fn(o_part, lse_part, s_aux, out_r.dtype)
+        attn_fn = attn_fn or _default_attn()
+        res = attn_fn(q, k_local, v_local, s_aux=s_aux, **common)
+        mark()
+        mark()
+        return res
+
+    total_q, hq = q.shape[0], q.shape[1]
+    hdv = v_local.shape[-1]
+    n_o, per = capi.partial_layout(total_q, hq, hdv)
+    if merge == "all_gather":
+        # every rank's slot of the gather buffer is its own send buffer: the kernel writes there, the collective
+        # runs in place, the merge kernel reads all slots where they lie.  The sink joins exactly once, in the merge.
+        gathered = torch.empty(world, per, device=q.device, dtype=torch.float32)
+        o_part = gathered[:, :n_o].view(world, total_q, hq, hdv)
+        lse_part = gathered[:, n_o:n_o + hq * total_q].view(world, hq, total_q)
+        partial_fn(q, k_local, v_local, out=o_part[rank], lse=lse_part[rank], s_aux=None, **common)
+        mark()
+        dist.all_gather_into_tensor(gathered.view(-1), gathered[rank], group=group)
+        res = combine_fn(o_part, lse_part, s_aux, out_dtype)
+        mark()
+        return res
+    if merge != "all_to_all":
+        raise ValueError(f"unknown merge mode {merge!r}")
+    if total_q % world != 0:
+        raise ValueError("merge='all_to_all' needs total_q divisible by the number of ranks")
+    rows = total_q // world
+    # O leaves the kernel as (total_q, hq, hdv): the rows of destination j are one contiguous block, so the
+    # exchange sends straight from the kernel's output.  The LSE is (hq, total_q); its (small) per-destination
+    # blocks are gathered into send order first.
+    o_r = torch.empty(total_q, hq, hdv, device=q.device, dtype=torch.float32)
+    lse_r = torch.empty(hq, total_q, device=q.device, dtype=torch.float32)
+    partial_fn(q, k_local, v_local, out=o_r, lse=lse_r, s_aux=None, **common)
+    mark()
+    o_recv = torch.empty(world, rows, hq, hdv, device=q.device, dtype=torch.float32)
+    dist.all_to_all_single(o_recv.view(-1), o_r.view(-1), group=group)
+    lse_send = lse_r.view(hq, world, rows).permute(1, 0, 2).contiguous()
+    lse_recv = torch.empty(world, hq, rows, device=q.device, dtype=torch.float32)
+    dist.all_to_all_single(lse_recv.view(-1), lse_send.view(-1), group=group)
+    out_j, lse_j = combine_fn(o_recv, lse_recv, s_aux, out_dtype)       # this rank's query rows
+    out = torch.empty(total_q, hq, hdv, device=q.device, dtype=out_dtype)
+    dist.all_gather_into_tensor(out.view(-1), out_j.contiguous().view(-1), group=group)
+    lse_all = torch.empty(world, hq, rows, device=q.device, dtype=torch.float32)
+    dist.all_gather_into_tensor(lse_all.view(-1), lse_j.contiguous().view(-1), group=group)
+    lse = lse_all.permute(1, 0, 2).reshape(hq, total_q)
+    mark()
+    return out, lse

@@ -30,22 +30,36 @@ enum {
   FA_ERR_NO_DEVICE = 4,     /* no sm_100 device / driver entry point missing */
   FA_ERR_LAUNCH = 5,        /* a CUDA call failed; see fa_b200_last_cuda_error() */
   FA_ERR_DEVICE_TIMEOUT = 6, /* a bounded device-side wait ran out (read from the status word) */
-  FA_ERR_STATIC_LIMIT = 7    /* problem needs more scratch than the built-in array of fa_b200_decode_fwd_static */
+  FA_ERR_STATIC_LIMIT = 7,   /* problem needs more scratch than the built-in array of fa_b200_decode_fwd_static */
+  FA_ERR_BAD_METADATA = 8    /* scheduler_metadata was made for another problem (read from the status word) */
 };
 
-enum { FA_DT_BF16 = 0, FA_DT_FP16 = 1, FA_DT_FP8_E4M3 = 2 };
+/* FA_DT_FP32 is an OUTPUT type only: `out` then receives the normalised result in fp32 (the form a partial
+ * result travels in before fa_b200_combine merges it; see fa_b200_combine_strided). */
+enum { FA_DT_BF16 = 0, FA_DT_FP16 = 1, FA_DT_FP8_E4M3 = 2, FA_DT_FP32 = 3 };
+
+/* FaFwdParams.flags */
+enum {
+  /* The caller promises that the first 256 bytes of `workspace` are zero when the call runs on its stream:
+   * zeroed once after allocation and since then used only by this library, one call at a time (every
+   * successful call leaves them zero again).  The library then issues no memset for them. */
+  FA_FLAG_WORKSPACE_CLEAN = 1
+};
 
 /* Which kernel family to use. AUTO routes by shape; the others force one family (testing, A/B). */
 enum { FA_ROUTE_AUTO = 0, FA_ROUTE_PREFILL_TC = 1, FA_ROUTE_DECODE = 2, FA_ROUTE_GENERAL = 3 };
 
-/* One attention-forward problem. Strides are in ELEMENTS. Replaces the argument list of
+/* One attention-forward problem. Strides are in ELEMENTS.  K/V rows that a page or a tile holds beyond a
+ * sequence's end (the tail of its last page, the next sequence's rows) get weight zero, but they are still
+ * multiplied: they must hold finite values (as with the page-granular loads of the reference,
+ * kernels/fa4_blackwell.cu:8913-8916). Replaces the argument list of
  * `mha_fwd` (kernels/fa4_blackwell.cu:10081-10094) after tensor unpacking. */
 typedef struct FaFwdParams {
   /* ---- tensors ---- */
   const void* q;            /* (total_q, hq, hd) */
   const void* k;            /* non-paged (total_k, hkv, hd); paged (num_pages, page_size, hkv, hd) */
   const void* v;            /* non-paged (total_k, hkv, hdv); paged (num_pages, page_size, hkv, hdv) */
-  void* out;                /* (total_q, hq, hdv); element type out_dtype */
+  void* out;                /* (total_q, hq, hdv); element type out_dtype (q's type, bf16 for e4m3 q, or FA_DT_FP32) */
   float* lse;               /* (hq, total_q) fp32, natural log; -inf for rows that see nothing */
   int64_t q_row_stride, q_head_stride;
   int64_t k_row_stride, k_head_stride, k_page_stride; /* row = one token; page stride only when paged */
@@ -60,10 +74,14 @@ typedef struct FaFwdParams {
   const float* k_descale;
   const float* v_descale;
   const float* s_aux;           /* (hq) fp32 sink logits or NULL */
-  const int32_t* scheduler_metadata; /* output of fa_b200_get_scheduler_metadata for this problem, or NULL */
+  const int32_t* scheduler_metadata; /* output of fa_b200_get_scheduler_metadata for this problem, or NULL.
+                                      * The kernels compare its header (batch, tiles, splits, route) with the
+                                      * call before they index it; a mismatch ends the call without output and
+                                      * fa_b200_check_status returns FA_ERR_BAD_METADATA. */
   /* ---- sizes ---- */
   int32_t batch, total_q, total_k, hq, hkv, hd, hdv;
-  int32_t max_seqlen_q, max_seqlen_k;      /* upper bounds known on the host (0 = unknown: not allowed) */
+  int32_t max_seqlen_q, max_seqlen_k;      /* upper bounds known on the host (any upper bound is valid: the
+                                            * kernels read the true lengths from cu_seqlens / seqused_k) */
   int32_t page_size, num_pages, page_table_stride;
   int32_t descale_batch_stride, descale_head_stride; /* 0,0 broadcasts a scalar */
   int32_t q_dtype, kv_dtype, out_dtype;    /* FA_DT_* */
@@ -76,6 +94,10 @@ typedef struct FaFwdParams {
   int32_t num_splits;                      /* 0 = heuristic, 1 = never split, >1 = at most that many */
   int32_t sm_margin;                       /* SMs to leave free */
   int32_t route;                           /* FA_ROUTE_* */
+  int32_t scheduler_metadata_len;          /* int32 words behind scheduler_metadata (0 = not stated); a length
+                                            * that differs from fa_b200_scheduler_metadata_len of this problem
+                                            * is refused on the host with FA_ERR_BAD_METADATA */
+  int32_t flags;                           /* FA_FLAG_* */
 } FaFwdParams;
 
 /* Bytes of scratch fa_b200_fwd needs for `p` (split partials, work list, status word). Host-only
@@ -121,11 +143,27 @@ int fa_b200_combine(const float* o_part, const float* lse_part, int32_t nsplits,
                     int32_t hq, int32_t hdv, const float* s_aux, void* out, int64_t o_row_stride,
                     int64_t o_head_stride, int32_t out_dtype, float* lse, fa_stream_t stream);
 
+/* The same merge reading the partials where a gather left them: split s begins `o_split_stride` /
+ * `lse_split_stride` floats after split s-1 (a packed per-rank buffer [O_r | LSE_r] gathered from N ranks has
+ * both strides equal to the buffer length).  No counterpart in the reference (single GPU). */
+int fa_b200_combine_strided(const float* o_part, const float* lse_part, int64_t o_split_stride,
+                            int64_t lse_split_stride, int32_t nsplits, int32_t total_q, int32_t hq, int32_t hdv,
+                            const float* s_aux, void* out, int64_t o_row_stride, int64_t o_head_stride,
+                            int32_t out_dtype, float* lse, fa_stream_t stream);
+
 /* Reads the device status word of a workspace after synchronising `stream` (the only entry point that
- * synchronises). Returns FA_OK, or FA_ERR_DEVICE_TIMEOUT with *detail = (role<<24 | block) of the first
- * wait that gave up. The reference has no counterpart: its device waits are unbounded
- * (kernels/fa4_blackwell.cu:5732). */
+ * synchronises). Returns FA_OK, FA_ERR_DEVICE_TIMEOUT with *detail = (role<<24 | block) of the first
+ * wait that gave up, or FA_ERR_BAD_METADATA when a kernel refused the scheduler metadata. The reference has
+ * no counterpart: its device waits are unbounded (kernels/fa4_blackwell.cu:5732). */
 int fa_b200_check_status(void* workspace, fa_stream_t stream, uint32_t* detail /* host, may be NULL */);
+
+/* Self-test of the bounded-wait machinery: launches ONE thread block that waits, with the same wait routine
+ * the attention kernels use, on a barrier nobody ever arrives at, for at most `max_cycles` SM clock cycles
+ * (clamped to [1e4, 1e8]).  The wait gives up, records the time-out in the status word at the start of
+ * `workspace` (>= 256 bytes, zeroed on `stream` by this call) and the kernel returns by itself; nothing is in
+ * flight and nothing faults.  fa_b200_check_status then reports FA_ERR_DEVICE_TIMEOUT.  No counterpart in the
+ * reference. */
+int fa_b200_selftest_timeout(void* workspace, int64_t max_cycles, fa_stream_t stream);
 
 /* Paged decode without any allocation, for callers that cannot obtain device memory at call time: an
  * inference worker that handed every free byte of HBM to its KV-cache pool at start-up (a later cudaMalloc

@@ -58,11 +58,18 @@ def ref_attention(
     q_rows: Optional[Sequence[int]] = None,
     heads: Optional[Sequence[int]] = None,
     q_chunk: int = 256,
+    round_to: Optional[torch.dtype] = None,
 ):
     """Returns (out fp32 (total_q, hq, hdv), lse fp32 (hq, total_q)).
 
     With `q_rows` (global row indices into q) and/or `heads` (q-head indices) only those entries are
     computed; every other entry of the returned tensors is NaN.
+
+    `round_to` (bfloat16 / float16) turns this into the BASELINE of the reference harness' error criterion
+    (bench/scenarios.py:681-687, bench/eval.py:1269-1273; there the baseline is another kernel, in the test suite
+    that criterion comes from it is this: the same plain attention evaluated in the input dtype, without
+    upcasting): scores, probabilities and output are each rounded to that dtype.  A kernel passes when its
+    error against the fp32 result is at most twice (three times with softcap) the error of this baseline.
     """
     q = q.detach().cpu()
     k = k.detach().cpu()
@@ -141,6 +148,8 @@ def ref_attention(
                 if lp[b] > 0:
                     mask |= kpos < lp[b]
                 s = torch.einsum("nhd,kd->nhk", Qc, Kb) * softmax_scale
+                if round_to is not None:
+                    s = s.to(round_to).to(torch.float32)
                 if softcap and softcap > 0:
                     s = softcap * torch.tanh(s / softcap)
                 s = s.masked_fill(mask.view(n, 1, kl), float("-inf"))
@@ -153,9 +162,12 @@ def ref_attention(
                 l = p.sum(dim=-1)
                 if sink is not None:
                     l = l + torch.exp(sk - m_safe)
-                o = torch.einsum("nhk,kd->nhd", p, Vb)
                 inv = torch.where(l > 0, 1.0 / l, torch.zeros_like(l))
-                o = o * inv.unsqueeze(-1)
+                if round_to is None:
+                    o = torch.einsum("nhk,kd->nhd", p, Vb) * inv.unsqueeze(-1)
+                else:
+                    a = (p * inv.unsqueeze(-1)).to(round_to).to(torch.float32)
+                    o = torch.einsum("nhk,kd->nhd", a, Vb).to(round_to).to(torch.float32)
                 ls = torch.where(l > 0, m_safe + torch.log(l), torch.full_like(l, float("-inf")))
                 out[rr.view(-1, 1), torch.tensor(hs).view(1, -1)] = o
                 lse[torch.tensor(hs).view(-1, 1), rr.view(1, -1)] = ls.t()

@@ -20,6 +20,7 @@ from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
 MAGIC, VERSION, HEADER, SORT_MAX = 0x46413230, 1, 16, 8192
+COUNT_MAX = (1 << 18) - 1   # block counts above this do not fit the device sort key: the list stays unsorted
 ROUTE_AUTO, ROUTE_PREFILL_TC, ROUTE_DECODE, ROUTE_GENERAL = 0, 1, 2, 3
 DT_BF16, DT_FP16, DT_FP8 = 0, 1, 2
 # which kernel families the library under test ships (the planner only routes to these)
@@ -91,7 +92,7 @@ def prefill_tc_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> b
 def decode_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> bool:
     if q_dtype == DT_FP8 or (kv_dtype != q_dtype and kv_dtype != DT_FP8):
         return False
-    if (hd, hdv) != (128, 128):
+    if not ((hd, hdv) == (128, 128) or (kv_dtype != DT_FP8 and (hd, hdv) in ((64, 64), (192, 128)))):
         return False
     if not (page_size in (0, 16, 32) or page_size % 64 == 0):   # contiguous, pages that divide a 64-row TMA box, or whole boxes
         return False
@@ -161,7 +162,7 @@ def scheduler_metadata(plan: Plan, *, batch, max_seqlen_q, max_seqlen_k, q_lens:
         lo, hi = nblock_range(sk, pad, sk - sq + tok_min, sk - sq + tok_max, causal, wl, wr, plan.tile_n)
         entries.append((True, b, mt, lo, hi))
     words = [0] * (HEADER + 4 * E)
-    is_sorted = E <= SORT_MAX
+    is_sorted = E <= SORT_MAX and cdiv(max_seqlen_k, plan.tile_n) <= COUNT_MAX
     if is_sorted:
         valid = [(e, x) for e, x in enumerate(entries) if x[0]]
         valid.sort(key=lambda ex: (-(ex[1][4] - ex[1][3]), ex[0]))

@@ -18,6 +18,14 @@ def _oracle_attn(q, k, v, *, max_seqlen_q=None, max_seqlen_k=None, **kw):
     return out.to(torch.bfloat16), lse
 
 
+def _oracle_partial(q, k, v, *, out, lse, max_seqlen_q=None, max_seqlen_k=None, **kw):
+    """Stands in for the CUDA kernel in its partial form: normalised O in fp32 and the LSE, written into the
+    caller's views of the send buffer."""
+    o, l = ref_attention(q, k, v, **kw)
+    out.copy_(o)
+    lse.copy_(l)
+
+
 def _oracle_combine(o_part, lse_part, s_aux, out_dtype):
     out, lse = combine_partials(o_part, lse_part, s_aux)
     return out.to(out_dtype), lse
@@ -48,7 +56,7 @@ def _worker(rank, world, port, mode, ret):
             # one sequence, q_len 48 against 256 keys in pages of 16; rank r owns keys [128 r, 128 r + 128)
             page, K, ql = 16, 256, 48
             p = W.make_problem("mg_kv", [(ql, K)], hq=4, hkv=2, hd=64, causal=True, page_size=page,
-                               permute_pages=False, spare_pages=0, sink=(mode == "kv_sink"), seed=9)
+                               permute_pages=False, spare_pages=0, sink=(mode != "kv"), seed=9)
             per = K // world
             pages = slice(rank * per // page, (rank + 1) * per // page)
             k_loc, v_loc = p.k[pages].contiguous(), p.v[pages].contiguous()
@@ -56,8 +64,9 @@ def _worker(rank, world, port, mode, ret):
             out, lse = MG.fwd_kv_sharded(
                 p.q, k_loc, v_loc, page_table_local=pt, seqused_k_local=torch.tensor([per], dtype=torch.int32),
                 cu_seqlens_q=p.cu_seqlens_q, max_seqlen_q=ql, max_seqlen_k_local=per,
-                softmax_scale=p.softmax_scale, causal=True, rank=rank, world=world, attn_fn=_oracle_attn,
-                combine_fn=_oracle_combine, s_aux=p.s_aux)
+                softmax_scale=p.softmax_scale, causal=True, rank=rank, world=world, partial_fn=_oracle_partial,
+                combine_fn=_oracle_combine, s_aux=p.s_aux,
+                merge="all_to_all" if mode == "kv_a2a" else "all_gather")
             ref_out, ref_lse = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
             ok = (out.float() - ref_out).abs().max().item() < 2e-2 and torch.allclose(lse, ref_lse, atol=1e-2)
         ret[rank] = bool(ok)
@@ -65,7 +74,7 @@ def _worker(rank, world, port, mode, ret):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["heads", "kv", "kv_sink"])
+@pytest.mark.parametrize("mode", ["heads", "kv", "kv_sink", "kv_a2a"])
 def test_two_rank_sharding_matches_single_rank(mode):
     world = 2
     mgr = mp.Manager()

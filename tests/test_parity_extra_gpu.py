@@ -1,0 +1,255 @@
+"""More GPU parity cases, through the C ABI, against the CPU oracle:
+
+  * the reference harness' RELATIVE error criterion (bench/scenarios.py:681-687, bench/eval.py:1269-1273):
+    max|out - ref| <= mult * max|baseline - ref| + fwd_atol, mult = 2 (3 with softcap),
+    fwd_atol = 2 * max|(ref + 0.3 - 0.3) - ref|, where the baseline is the plain attention evaluated in the input
+    dtype (the form of the criterion that needs no second kernel);
+  * shapes the router accepts that the fixtures do not reach: page sizes 1 / 2 / 4 / 8, the tensor-core prefill
+    kernel over pages of 16 .. 256 keys, head_dim 192 with 192 value columns, fp16 queries over an e4m3 cache,
+    decode at head_dim 64 and 192/128, a q_descale that is not 1 with 16-bit queries;
+  * e4m3 prefill: full-tensor error of the tensor-core route against the oracle, with the margin asserted;
+  * scheduler metadata: consumed by the prefill route, refused when it belongs to another problem;
+  * the bounded-wait path: a wait that nobody satisfies ends by itself with an error code.
+"""
+import pytest
+import torch
+
+import _golden
+from flash_cuda_b200 import capi, workloads as W
+from oracle.ref_attention import ref_attention
+
+pytestmark = pytest.mark.gpu
+
+TC, DEC, GEN, AUTO = capi.FA_ROUTE_PREFILL_TC, capi.FA_ROUTE_DECODE, capi.FA_ROUTE_GENERAL, capi.FA_ROUTE_AUTO
+
+
+def _check(p, dev, route, tol, lse_atol=5e-3, **extra):
+    ref_out, ref_lse = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
+    pd = p.to(dev)
+    out, lse, _ = capi.fwd(pd.q, pd.k, pd.v, route=route, check=True, **dict(pd.capi_kw(), **extra))
+    out, lse = out.float().cpu(), lse.cpu()
+    assert torch.isfinite(out).all(), p.name
+    err = (out - ref_out).abs().max().item()
+    assert err <= tol, f"{p.name}: max-abs error {err:.4g} > {tol}"
+    fin = torch.isfinite(ref_lse)
+    assert torch.equal(torch.isfinite(lse), fin), p.name
+    torch.testing.assert_close(lse[fin], ref_lse[fin], atol=lse_atol, rtol=1e-2)
+    return err
+
+
+# ---------------------------------------------------------------------------------------------------------
+# relative criterion
+# ---------------------------------------------------------------------------------------------------------
+SIXTEEN_BIT = [n for n in _golden.NAMES if "fp8" not in n]
+
+
+@pytest.mark.parametrize("name", SIXTEEN_BIT)
+def test_error_at_most_twice_the_in_dtype_baseline(name, cuda_device):
+    d = _golden.load(name)
+    assert d["q"].dtype in (torch.bfloat16, torch.float16) and d["k"].dtype == d["q"].dtype
+    cfg = d["cfg"]
+    ref = d["ref_out"]
+    base, _ = ref_attention(d["q"], d["k"], d["v"], round_to=d["q"].dtype, **_golden.oracle_kwargs(d))
+    kw = dict(cu_seqlens_q=d["cu_seqlens_q"], cu_seqlens_k=d["cu_seqlens_k"], seqused_k=d["seqused_k"],
+              page_table=d["page_table"], leftpad_k=d["leftpad_k"], s_aux=d["s_aux"] if cfg["sink"] else None)
+    kw = {n: (None if t is None else t.to(cuda_device)) for n, t in kw.items()}
+    out, _, _ = capi.fwd(d["q"].to(cuda_device), d["k"].to(cuda_device), d["v"].to(cuda_device), check=True,
+                         max_seqlen_q=d["max_seqlen_q"], max_seqlen_k=d["max_seqlen_k"],
+                         softmax_scale=d["softmax_scale"], causal=bool(cfg["causal"]),
+                         window_left=int(cfg["window_left"]), window_right=int(cfg["window_right"]),
+                         softcap=float(cfg["softcap"]), num_splits=int(cfg["num_splits"]), **kw)
+    mult = 3.0 if float(cfg["softcap"]) > 0 else 2.0
+    fwd_atol = 2.0 * (ref + 0.3 - 0.3 - ref).abs().max().item()
+    err = (out.float().cpu() - ref).abs().max().item()
+    base_err = (base - ref).abs().max().item()
+    assert err <= mult * base_err + fwd_atol, f"{name}: err {err:.3e} > {mult} x baseline {base_err:.3e} + {fwd_atol:.1e}"
+
+
+@pytest.mark.parametrize("route", [AUTO, GEN])
+def test_relative_criterion_on_benchmark_shapes(route, cuda_device):
+    probs = [W.causal_gqa_prefill(B=1, S=1024), W.dense_noncausal(B=1, H=4, S=512),
+             W.varlen_window_softcap_sink(n=3, lo=100, hi=700, window=256), W.paged_decode(B=8, ctx_lo=200, ctx_hi=3000)]
+    for p in probs:
+        ref, _ = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
+        base, _ = ref_attention(p.q, p.k, p.v, round_to=p.q.dtype, **p.oracle_kw())
+        pd = p.to(cuda_device)
+        out, _, _ = capi.fwd(pd.q, pd.k, pd.v, route=route, check=True, **pd.capi_kw())
+        mult = 3.0 if p.softcap > 0 else 2.0
+        err = (out.float().cpu() - ref).abs().max().item()
+        base_err = (base - ref).abs().max().item()
+        assert err <= mult * base_err + 2.0 * (ref + 0.3 - 0.3 - ref).abs().max().item(), (p.name, err, base_err)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# shapes outside the fixtures
+# ---------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("page_size", [1, 2, 4, 8])
+def test_small_pages(page_size, cuda_device):
+    """Pages smaller than a TMA box: decode-shaped and prefill-shaped batches (AUTO picks the route)."""
+    dec = W.make_problem(f"small_pages_dec{page_size}", [(1, 333), (1, 64), (2, 129), (1, 1)], hq=8, hkv=2, hd=128,
+                         causal=True, page_size=page_size, leftpad=[7, 0, 0, 0], sink=True, seed=41)
+    pre = W.make_problem(f"small_pages_pre{page_size}", [(200, 200), (40, 300)], hq=4, hkv=2, hd=128, causal=True,
+                         page_size=page_size, seed=42)
+    for p in (dec, pre):
+        _check(p, cuda_device, AUTO, 2e-2)
+
+
+@pytest.mark.parametrize("page_size", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("dtype", ["bf16", "fp8"])
+def test_tensor_core_prefill_over_pages(page_size, dtype, cuda_device):
+    """The tcgen05 prefill kernel forced onto paged KV: pages that divide a 128-key tile and pages that hold
+    one or two whole tiles; ragged lengths, a chunk (q_len < k_len) and leftpad."""
+    p = W.make_problem(f"tc_pages_{dtype}_{page_size}", [(300, 300), (130, 700), (256, 257), (5, 1000)], hq=4, hkv=2,
+                       hd=128, dtype=dtype, causal=True, page_size=page_size, leftpad=[0, 70, 0, 129], seed=43)
+    _check(p, cuda_device, TC, 6e-2 if dtype == "fp8" else 2e-2)
+
+
+def test_head_dim_192_with_192_value_columns(cuda_device):
+    p = W.make_problem("hd192_192", [(150, 150), (33, 400)], hq=4, hkv=2, hd=192, hdv=192, causal=True, seed=44)
+    _check(p, cuda_device, AUTO, 2e-2)
+    pp = W.make_problem("hd192_192_paged", [(1, 500), (3, 260)], hq=4, hkv=2, hd=192, hdv=192, causal=True,
+                        page_size=64, seed=45)
+    _check(pp, cuda_device, AUTO, 2e-2)
+
+
+@pytest.mark.parametrize("route", [AUTO, DEC, GEN])
+def test_fp16_queries_over_e4m3_cache(route, cuda_device):
+    p = W.make_problem("fp16q_fp8kv", [(1, 900), (2, 2100), (1, 64)], hq=16, hkv=4, hd=128, dtype="fp16",
+                       kv_dtype="fp8", causal=True, page_size=64, leftpad=[3, 0, 63], sink=True, seed=46)
+    _check(p, cuda_device, route, 6e-2)
+
+
+@pytest.mark.parametrize("hd,hdv", [(64, 64), (192, 128)])
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+def test_decode_route_head_dims(hd, hdv, dtype, cuda_device):
+    """The streaming decode kernel at the other head dims of the reference's paged kernel
+    (kernels/fa4_blackwell.cu:9958-9983), pages of 16 and 64 keys, contiguous K/V, splits."""
+    for page_size in (64, 16, 0):
+        p = W.make_problem(f"dec_hd{hd}_{dtype}_p{page_size}", [(1, 1000), (2, 130), (1, 64), (1, 3)], hq=8, hkv=2,
+                           hd=hd, hdv=hdv, dtype=dtype, causal=True, page_size=page_size,
+                           leftpad=[9, 0, 0, 1] if page_size else None, sink=True, seed=47)
+        _check(p, cuda_device, DEC, 2e-2)
+        _check(p, cuda_device, DEC, 2e-2, num_splits=3)
+    pa = W.make_problem(f"dec_hd{hd}_auto", [(1, 3000)] * 3, hq=8, hkv=2, hd=hd, hdv=hdv, dtype=dtype, page_size=64, seed=48)
+    _check(pa, cuda_device, AUTO, 2e-2)
+
+
+@pytest.mark.parametrize("route", [DEC, GEN, AUTO])
+def test_q_descale_with_16_bit_queries(route, cuda_device):
+    """q_descale multiplies the logits whatever the type of Q (kernels/fa3_hopper.cu:101-108): every route must
+    apply it, also the decode route, where Q is never e4m3."""
+    p = W.make_problem("qdescale", [(1, 700), (2, 300)], hq=8, hkv=2, hd=128, kv_dtype="fp8", causal=True,
+                       page_size=64, seed=49)
+    qd = torch.tensor([[0.5, 1.7], [2.0, 0.25]], dtype=torch.float32)
+    p.q_descale = qd
+    _check(p, cuda_device, route, 6e-2)
+
+
+def test_e4m3_prefill_full_tensor_error_has_margin(cuda_device):
+    """All-e4m3 causal prefill on the tensor-core route (P is rounded to e4m3 for the PV product): the error over
+    the WHOLE output against the fp32 oracle, not a sample.  The limit of the benchmark definition is 6e-2; the
+    kernel has to stay below 4.5e-2 here so that another seed does not tip it over."""
+    worst = 0.0
+    for seed in (0, 1, 2):
+        p = W.causal_gqa_prefill(B=1, S=1536, dtype="fp8", seed=seed)
+        worst = max(worst, _check(p, cuda_device, TC, 6e-2))
+    print(f"e4m3 prefill full-tensor max error over 3 seeds: {worst:.4g}")
+    assert worst <= 4.5e-2
+
+
+# ---------------------------------------------------------------------------------------------------------
+# scheduler metadata
+# ---------------------------------------------------------------------------------------------------------
+def _metadata_for(p, dev, **over):
+    hq, hd = p.q.shape[1], p.q.shape[2]
+    paged = p.page_table is not None
+    kw = dict(batch=len(p.q_lens), max_seqlen_q=p.max_seqlen_q, max_seqlen_k=p.max_seqlen_k, hq=hq,
+              hkv=p.k.shape[-2], hd=hd, hdv=p.v.shape[-1], dtype=p.q.dtype,
+              seqused_k=None if p.seqused_k is None else p.seqused_k.to(dev),
+              cu_seqlens_q=p.cu_seqlens_q.to(dev), cu_seqlens_k=None if p.cu_seqlens_k is None else p.cu_seqlens_k.to(dev),
+              leftpad_k=None if p.leftpad_k is None else p.leftpad_k.to(dev), page_size=p.k.shape[1] if paged else 0,
+              causal=p.causal, window_left=p.window_left, window_right=p.window_right, has_softcap=p.softcap > 0)
+    kw.update(over)
+    return capi.get_scheduler_metadata(dev, **kw)
+
+
+def test_prefill_route_consumes_scheduler_metadata(cuda_device):
+    """Ragged batch on the tensor-core route: with the metadata the kernel walks the sorted (batch, tile) list,
+    without it the arithmetic order; both give the oracle's numbers."""
+    p = W.make_problem("md_prefill", [(700, 700), (30, 30), (257, 900), (0, 10), (1300, 1300)], hq=4, hkv=2, hd=128,
+                       causal=True, window_left=500, window_right=0, seed=51)
+    md = _metadata_for(p, cuda_device)
+    assert int(md[9]) == TC and int(md[4]) == 256
+    _check(p, cuda_device, TC, 2e-2)
+    _check(p, cuda_device, TC, 2e-2, scheduler_metadata=md)
+    _check(p, cuda_device, AUTO, 2e-2, scheduler_metadata=md)
+
+
+@pytest.mark.parametrize("kind", ["decode", "prefill"])
+def test_metadata_of_another_problem_is_refused(kind, cuda_device):
+    """Metadata built for batch 5 handed to a batch-3 call.  It is long enough that no read could leave the
+    tensor; the kernel must still not index it: the header check records the mismatch, the kernel produces
+    nothing, and the status call reports FA_ERR_BAD_METADATA."""
+    if kind == "decode":
+        big = W.make_problem("md5", [(1, 500)] * 5, hq=8, hkv=2, hd=128, causal=True, page_size=64, seed=52)
+        small = W.make_problem("md3", [(1, 500)] * 3, hq=8, hkv=2, hd=128, causal=True, page_size=64, seed=53)
+    else:
+        big = W.make_problem("mp5", [(300, 300)] * 5, hq=4, hkv=2, hd=128, causal=True, seed=52)
+        small = W.make_problem("mp3", [(300, 300)] * 3, hq=4, hkv=2, hd=128, causal=True, seed=53)
+    md_big = _metadata_for(big, cuda_device)
+    pd = small.to(cuda_device)
+    # stated length: refused on the host
+    with pytest.raises(capi.FaError) as ei:
+        capi.fwd(pd.q, pd.k, pd.v, scheduler_metadata=md_big, **pd.capi_kw())
+    assert ei.value.code == capi.FA_ERR_BAD_METADATA
+    # length not stated (a binding that passes only the pointer): refused on the device
+    out = torch.zeros(pd.q.shape[0], pd.q.shape[1], 128, device=cuda_device, dtype=torch.bfloat16)   # kept alive: the
+    lse = torch.zeros(pd.q.shape[1], pd.q.shape[0], device=cuda_device)                              # call is asynchronous
+    p_, keep = capi.make_params(pd.q, pd.k, pd.v, out, lse, scheduler_metadata=md_big, **pd.capi_kw())
+    p_.scheduler_metadata_len = 0
+    import ctypes as C
+    lib = capi.load()
+    ws = torch.empty(max(lib.fa_b200_fwd_workspace_bytes(C.byref(p_)), 256), device=cuda_device, dtype=torch.uint8)
+    rc = lib.fa_b200_fwd(C.byref(p_), ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream)
+    assert rc == capi.FA_OK
+    with pytest.raises(capi.FaError) as ei:
+        capi.check_status(ws)
+    assert ei.value.code == capi.FA_ERR_BAD_METADATA, f"status detail {getattr(ei.value, 'detail', 0):#x}"
+    # the library is still usable and the same call without the foreign metadata is right
+    _check(small, cuda_device, AUTO, 2e-2)
+
+
+def test_metadata_round_trip_same_problem_decode(cuda_device):
+    p = W.paged_decode(B=9, ctx_lo=100, ctx_hi=5000)
+    md = _metadata_for(p, cuda_device)
+    assert int(md[9]) == DEC
+    _check(p, cuda_device, AUTO, 2e-2, scheduler_metadata=md)
+
+
+# ---------------------------------------------------------------------------------------------------------
+# bounded waits
+# ---------------------------------------------------------------------------------------------------------
+def test_a_wait_nobody_satisfies_gives_up_with_an_error_code(cuda_device):
+    """One thread block waits (with the wait routine of the attention kernels) on a barrier that never
+    completes, with a budget of 2e5 SM cycles; it must return by itself and leave DEV_ERR_TIMEOUT with the
+    self-test role in the status word.  Nothing is in flight and nothing faults; the context stays usable."""
+    with torch.cuda.device(cuda_device):
+        ws = capi.selftest_timeout(cuda_device, max_cycles=200_000)
+        with pytest.raises(capi.FaError) as ei:
+            capi.check_status(ws)
+        assert ei.value.code == capi.FA_ERR_DEVICE_TIMEOUT
+        assert (ei.value.detail >> 24) == 7 and (ei.value.detail & 0xFFFFFF) == 0
+        # the device is fine afterwards
+        p = W.causal_gqa_prefill(B=1, S=256)
+        _check(p, cuda_device, AUTO, 2e-2)
+
+
+def test_maxima_may_be_upper_bounds(cuda_device):
+    """max_seqlen_q / max_seqlen_k are only bounds: larger values change the launch geometry, not the result."""
+    p = W.make_problem("bounds", [(100, 100), (300, 400)], hq=4, hkv=2, hd=128, causal=True, seed=54)
+    ref_out, _ = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
+    pd = p.to(cuda_device)
+    kw = dict(pd.capi_kw(), max_seqlen_q=pd.q.shape[0], max_seqlen_k=pd.k.shape[0])
+    for route in (AUTO, GEN):
+        out, _, _ = capi.fwd(pd.q, pd.k, pd.v, route=route, check=True, **kw)
+        assert (out.float().cpu() - ref_out).abs().max().item() <= 2e-2

@@ -3,7 +3,8 @@
 Some callers cannot obtain device memory when they call: a serving worker whose KV-cache pool already owns all
 free HBM, or a host in another language with no device allocator.  For them the library keeps the decode scratch
 in an 8 MiB array of its own.  The result must match the ordinary entry point (`fa_b200_fwd`, caller workspace) on
-the same inputs, call after call, because the array still holds the previous call's contents.
+the same inputs, call after call, because the array still holds the previous call's contents; and, so that the
+comparison is not the library against itself only, it must match the CPU oracle too.
 
 This file sorts last on purpose: a run that stops at the first failure has then already run every other test.
 """
@@ -11,6 +12,7 @@ import pytest
 import torch
 
 from flash_cuda_b200 import capi, workloads as W
+from oracle.ref_attention import ref_attention
 
 pytestmark = pytest.mark.gpu
 
@@ -28,8 +30,11 @@ def _problems():
 
 
 def test_static_scratch_decode_matches_workspace_decode(cuda_device):
+    oracle = {}
     for rounds in range(2):                       # two passes: every call finds the previous call's leftovers
         for p, nsplit in _problems():
+            if p.name not in oracle:
+                oracle[p.name] = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
             pd = p.to(cuda_device)
             kw = dict(pd.capi_kw(), num_splits=nsplit)
             ref_out, ref_lse, _ = capi.fwd(pd.q, pd.k, pd.v, route=capi.FA_ROUTE_DECODE, check=True, **kw)
@@ -40,6 +45,12 @@ def test_static_scratch_decode_matches_workspace_decode(cuda_device):
             fin = torch.isfinite(ref_lse)
             assert torch.equal(torch.isfinite(lse), fin)
             torch.testing.assert_close(lse[fin], ref_lse[fin], atol=5e-3, rtol=1e-2)
+            # ... and against the fp32 oracle, with the tolerance of the cache type
+            o_out, o_lse = oracle[p.name]
+            tol = 6e-2 if p.k.dtype == torch.float8_e4m3fn else 2e-2
+            assert (out.float().cpu() - o_out).abs().max().item() <= tol, p.name
+            ofin = torch.isfinite(o_lse)
+            torch.testing.assert_close(lse.cpu()[ofin], o_lse[ofin], atol=5e-3, rtol=1e-2)
 
 
 def test_static_scratch_rejects_what_does_not_fit(cuda_device):
@@ -48,8 +59,8 @@ def test_static_scratch_rejects_what_does_not_fit(cuda_device):
     with pytest.raises(capi.FaError) as ei:
         capi.decode_fwd_static(big.q, big.k, big.v, **dict(big.capi_kw(), num_splits=64))
     assert ei.value.code == capi.FA_ERR_STATIC_LIMIT and "8 MiB" in str(ei.value)
-    # a shape the decode route does not take (head_dim 64) is refused, not rerouted
-    dense = W.make_problem("na_dense", [(4, 64)], hq=4, hkv=4, hd=64, page_size=64, seed=25).to(cuda_device)
+    # a shape the decode route does not take (head_dim 256) is refused, not rerouted
+    dense = W.make_problem("na_dense", [(4, 64)], hq=4, hkv=4, hd=256, page_size=64, seed=25).to(cuda_device)
     with pytest.raises(capi.FaError) as ei:
         capi.decode_fwd_static(dense.q, dense.k, dense.v, **dense.capi_kw())
     assert ei.value.code == capi.FA_ERR_UNSUPPORTED
