@@ -31,6 +31,7 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "fa_internal.h"
@@ -88,7 +89,7 @@ struct Smem {
   static constexpr bool kStageOut = kRings + kStageBytes + 3 * 1024 <= kSmemLimit;
   static constexpr int kStageOff = kRings;
   static constexpr int kBarOff = kRings + (kStageOut ? kStageBytes : 0);
-  static constexpr int kNumBars = 2 + KST + 2 * VST + 8 + 1 + 4 + 1 + KST;
+  static constexpr int kNumBars = 4 + KST + 2 * VST + 8 + 1 + 4 + 1 + KST;
   static constexpr int kItemOff = kBarOff + ((kNumBars * 8 + 16 + 15) & ~15);   // after abort flags and TMEM base
   static constexpr int kBytes = kItemOff + 2 * 64;             // two mailbox slots of one decoded work item each
 };
@@ -183,8 +184,8 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   const uint32_t sV = sK + KST * SM::kKStage;
   const uint32_t bars = base + SM::kBarOff;
   // barrier map
-  const uint32_t bar_q_full = bars, bar_q_empty = bars + 8;
-  const uint32_t bar_k_empty = bars + 16;                // [KST] (K tiles complete on k0_full / v_full, see the TMA role)
+  const uint32_t bar_q_full = bars, bar_q_empty = bars + 16;   // [2] each: one per query tile
+  const uint32_t bar_k_empty = bars + 32;                // [KST] (K tiles complete on k0_full / v_full, see the TMA role)
   const uint32_t bar_v_full = bar_k_empty + 8 * KST, bar_v_empty = bar_v_full + 8 * VST;
   const uint32_t bar_s_full = bar_v_empty + 8 * VST;     // [2]
   const uint32_t bar_p_full = bar_s_full + 16;           // [2]
@@ -206,7 +207,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   if (tid == 0) {
-    mbar_init(bar_q_full, 1); mbar_init(bar_q_empty, 1);
+    for (int t = 0; t < 2; ++t) { mbar_init(bar_q_full + 8 * t, 1); mbar_init(bar_q_empty + 8 * t, 1); }
     for (int s = 0; s < KST; ++s) mbar_init(bar_k_empty + 8 * s, 1);
     for (int s = 0; s < VST; ++s) { mbar_init(bar_v_full + 8 * s, 1); mbar_init(bar_v_empty + 8 * s, 1); }
     for (int t = 0; t < 2; ++t) {
@@ -287,16 +288,20 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         // the next item is fetched one ahead, but only after this item's first loads are on their way: the
         // counter round trip and the decoding then hide behind them
         if (it.uhi <= it.ulo) { it_next = fetch_and_publish(); continue; }   // rows without keys: only an epilogue
-        ok = wait_or_abort(bar_q_empty, (qcnt & 1) ^ 1, s_abort);
-        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
-        mbar_expect_tx(bar_q_full, SM::kQBytes);
-#pragma unroll
-        for (int t = 0; t < 2; ++t)
+        // Each query tile has its own pair of barriers: tile 0 usually finishes an item one key block before tile 1
+        // (causal masking), so its Q slot is free, and refilled, a block earlier; the next item's first loads are
+        // then spread over two blocks instead of one.  Order: Q tile 0, K of the first block, Q tile 1.
+        auto load_q = [&](int t) -> bool {
+          if (!wait_or_abort(bar_q_empty + 8 * t, (qcnt & 1) ^ 1, s_abort)) return false;
+          mbar_expect_tx(bar_q_full + 8 * t, SM::kQBytes / 2);
 #pragma unroll
           for (int cb = 0; cb < HD / EPB; ++cb)
             tma_load_3d(sQ + t * (TM * HD * ESZ) + cb * (TM * 128), &map_q, cb * EPB, it.h,
-                        it.q0 + it.pair * 2 * TM + t * TM, bar_q_full);
-        ++qcnt;
+                        it.q0 + it.pair * 2 * TM + t * TM, bar_q_full + 8 * t);
+          return true;
+        };
+        ok = load_q(0);
+        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
         const int hk = it.h / p.rep;
         // one K or V tile of key block nb into `dst`, completing on `bar`
         auto load_tile = [&](const CUtensorMap* map, int width, uint32_t dst, int nb, uint32_t bar) {
@@ -328,6 +333,9 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           kr.advance();
           ++k0cnt;
         }
+        ok = load_q(1);
+        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+        ++qcnt;
         for (int nb = it.ulo; nb < it.uhi; ++nb) {
           const bool nxt = nb + 1 < it.uhi;
           const uint32_t vs = vr.slot, ks = kr.slot;
@@ -348,7 +356,10 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       }
       if (!ok) *s_abort = 1;
       // drain: every copy this thread issued must have landed before the CTA may leave
-      if (qcnt > 0) wait_or_abort(bar_q_full, (qcnt - 1) & 1, s_abort + 1 /* never set: pure time limit */);
+      if (qcnt > 0) {
+        wait_or_abort(bar_q_full, (qcnt - 1) & 1, s_abort + 1 /* never set: pure time limit */);
+        wait_or_abort(bar_q_full + 8, (qcnt - 1) & 1, s_abort + 1);
+      }
       if constexpr (MERGE_KV) {
         if (k0cnt > 0) wait_or_abort(bar_k0_full, (k0cnt - 1) & 1, s_abort + 1);
       } else {
@@ -429,23 +440,28 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     };
     auto commit = [&](uint32_t bar) { if (leader) umma_commit(bar); };
 
+    // One decoded work item as this warp needs it (block ranges, broadcast so that every loop bound is warp-uniform).
+    struct MItem { int lo[2], hi[2], ulo, uhi, valid, w; };
     uint32_t wcnt = 0;
-    while (true) {
+    auto read_item = [&]() -> MItem {
       const uint32_t slot = wcnt & 1;
       wait(bar_w_full + 8 * slot, (wcnt >> 1) & 1);
       const int4 ra = reinterpret_cast<const int4*>(&s_item[slot])[2], rb = reinterpret_cast<const int4*>(&s_item[slot])[3];
-      // block ranges, broadcast so that every loop bound below is warp-uniform
-      const int lo0 = __shfl_sync(FULL, ra.x, 0), lo1 = __shfl_sync(FULL, ra.y, 0);
-      const int hi0 = __shfl_sync(FULL, ra.z, 0), hi1 = __shfl_sync(FULL, ra.w, 0);
-      const int ulo = __shfl_sync(FULL, rb.x, 0), uhi = __shfl_sync(FULL, rb.y, 0);
-      const int valid = __shfl_sync(FULL, rb.z, 0), w = __shfl_sync(FULL, rb.w, 0);
+      MItem m;
+      m.lo[0] = __shfl_sync(FULL, ra.x, 0); m.lo[1] = __shfl_sync(FULL, ra.y, 0);
+      m.hi[0] = __shfl_sync(FULL, ra.z, 0); m.hi[1] = __shfl_sync(FULL, ra.w, 0);
+      m.ulo = __shfl_sync(FULL, rb.x, 0); m.uhi = __shfl_sync(FULL, rb.y, 0);
+      m.valid = __shfl_sync(FULL, rb.z, 0); m.w = __shfl_sync(FULL, rb.w, 0);
       if (leader) mbar_arrive(bar_w_empty + 8 * slot);
       ++wcnt;
-      if (__any_sync(FULL, fail) || w == kEndOfWork) break;
-      if (!valid || uhi <= ulo) continue;
-      const int lo[2] = {lo0, lo1}, hi[2] = {hi0, hi1};
-      wait(bar_q_full, qcnt & 1);
-      ++qcnt;
+      return m;
+    };
+    while (true) {
+      const MItem cur = read_item();
+      if (__any_sync(FULL, fail) || cur.w == kEndOfWork) break;
+      if (!cur.valid || cur.uhi <= cur.ulo) continue;
+      const int ulo = cur.ulo, uhi = cur.uhi;
+      const int lo[2] = {cur.lo[0], cur.lo[1]}, hi[2] = {cur.hi[0], cur.hi[1]};
       // prologue: QK of the first block
       {
         const uint32_t ks = kr.slot;
@@ -453,11 +469,15 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         else wait(bar_k_full + 8 * ks, kr.phase);
         ++k0cnt;
 #pragma unroll
-        for (int t = 0; t < 2; ++t)
+        for (int t = 0; t < 2; ++t) {
+          wait(bar_q_full + 8 * t, qcnt & 1);
           if (ulo >= lo[t] && ulo < hi[t]) issue_qk(t, ks);
+          // tile t's only QK of this item (or it has none): its Q slot may be refilled once that has run
+          if (hi[t] <= lo[t] || hi[t] - 1 <= ulo) commit(bar_q_empty + 8 * t);
+        }
+        ++qcnt;
         commit(bar_k_empty + 8 * ks);
         kr.advance();
-        if (ulo + 1 == uhi) commit(bar_q_empty);   // that was the item's only QK: Q may be replaced once it has run
       }
       for (int i = ulo; i < uhi; ++i) {
         const bool nxt = i + 1 < uhi;
@@ -482,10 +502,10 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           if (nxt && i + 1 >= lo[t] && i + 1 < hi[t]) {
             if (!k_ready) { wait(bar_k_full + 8 * ks, kr.phase); k_ready = true; }
             issue_qk(t, ks);
+            // tile t's last QK of the item: its Q slot is refilled during the item's remaining blocks
+            if (i + 2 == hi[t]) commit(bar_q_empty + 8 * t);
           }
         }
-        // the item's last QK has been issued: the next item's Q tiles load during this item's last block
-        if (i + 2 == uhi) commit(bar_q_empty);
         commit(bar_v_empty + 8 * vs);
         vr.advance();
         if (nxt) {

@@ -32,12 +32,15 @@ def _worker(rank, world, port, ret):
         pages = slice(rank * per // page, (rank + 1) * per // page)
         k_loc, v_loc = full.k[pages].contiguous(), full.v[pages].contiguous()
         pt = torch.arange(per // page, device=dev, dtype=torch.int32).view(1, -1)
-        out, lse = MG.fwd_kv_sharded(full.q, k_loc, v_loc, page_table_local=pt,
-                                     seqused_k_local=torch.tensor([per], device=dev, dtype=torch.int32),
-                                     cu_seqlens_q=full.cu_seqlens_q, max_seqlen_q=q_len, max_seqlen_k_local=per,
-                                     softmax_scale=full.softmax_scale, causal=True, rank=rank, world=world)
-        ok_kv = (out.float() - ref_out.float()).abs().max().item() <= 1e-2 and \
-            (lse - ref_lse).abs().max().item() <= 2e-3
+        ok_kv = True
+        for merge in ("all_gather", "all_to_all"):
+            out, lse = MG.fwd_kv_sharded(full.q, k_loc, v_loc, page_table_local=pt,
+                                         seqused_k_local=torch.tensor([per], device=dev, dtype=torch.int32),
+                                         cu_seqlens_q=full.cu_seqlens_q, max_seqlen_q=q_len, max_seqlen_k_local=per,
+                                         softmax_scale=full.softmax_scale, causal=True, rank=rank, world=world,
+                                         merge=merge)
+            ok_kv = ok_kv and (out.float() - ref_out.float()).abs().max().item() <= 1e-2 and \
+                (lse - ref_lse).abs().max().item() <= 2e-3
         # --- head sharding: each rank its block of kv heads, outputs are the matching slices
         p = W.make_problem("mg", [(300, 300), (40, 700)], hq=8, hkv=4, hd=128, causal=True, seed=6).to(dev)
         ref2, lse2 = ops.call_fwd(p.q, p.k, p.v, **p.capi_kw())
