@@ -43,8 +43,9 @@ enum : int { F_FIRST = 1, F_LAST = 2, F_EMPTY = 4 };
 struct DecArgs {
   KParams kp;
   int total_work;     // num_work * hkv * nsplits
-  int box_rows;       // rows per TMA box = min(page_size, 64)
+  int box_rows;       // rows per TMA box = min(page_size, 64); 1 in gather mode
   int kv_total_rows;
+  int gather;         // pages of 1, 2 or 4 keys: rows are fetched four at a time with tile::gather4
 };
 
 template <int ESZ, int NST, int HD, int HDV>
@@ -183,6 +184,55 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
       const int npages = (it.seqlen_k + ps - 1) / ps;
       int cache_first = -1, cache_id = 0;       // 32 page-table entries, one per lane
       const int key_end = it.hi * TN;
+      if (a.gather) {
+        // Pages smaller than a TMA box: lane g < 16 owns keys 4g..4g+3 of every stage, looks their physical rows up
+        // itself (before it waits for the stage, so that the lookups overlap the wait) and issues one gather4 per
+        // 128-byte column block of K and V.  Keys beyond the sequence fetch pool row 0 and are masked by the consumers.
+        const int32_t* pt = p.page_table + (int64_t)it.b * p.page_table_stride;
+        for (int key0 = it.lo * TN; key0 < key_end && ok; key0 += TNS) {
+          int y[4] = {0, 0, 0, 0};
+          if (lane < TNS / 4) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int kk = key0 + 4 * lane + j;
+              if (kk < it.seqlen_k && kk < key_end) {
+                const int lp = kk / ps;
+                y[j] = pt[lp] * ps + (kk - lp * ps);
+              }
+            }
+          }
+          const uint32_t s = cnt % NST;
+          ok = wait_or_abort(bar_empty + 8 * s, ((cnt / NST) & 1) ^ 1, s_abort);
+          if (!ok) break;
+          const uint32_t kdst = base + s * SM::kStage, vdst = kdst + SM::kKBytes;
+          if (lane == 0) {
+            int flags = 0;
+            if (key0 == it.lo * TN) flags |= F_FIRST;
+            if (key0 + TNS >= key_end) flags |= F_LAST;
+            s_info[4 * s] = w; s_info[4 * s + 1] = key0; s_info[4 * s + 2] = flags;
+            mbar_expect_tx(bar_full + 8 * s, SM::kStage);
+          }
+          __syncwarp();
+          if (lane < TNS / 4) {
+            const uint32_t roff = (uint32_t)(4 * lane) * 128u;
+            if (KV8) {
+              tma_gather4_2d(kdst + roff, &map_k, it.hk * HD, y[0], y[1], y[2], y[3], bar_full + 8 * s);
+              tma_gather4_2d(vdst + roff, &map_v, it.hk * HDV, y[0], y[1], y[2], y[3], bar_full + 8 * s);
+            } else {
+#pragma unroll
+              for (int cb = 0; cb < HD / 64; ++cb)
+                tma_gather4_2d(kdst + cb * (TNS * 128) + roff, &map_k, it.hk * HD + cb * 64, y[0], y[1], y[2], y[3],
+                               bar_full + 8 * s);
+#pragma unroll
+              for (int cb = 0; cb < HDV / 64; ++cb)
+                tma_gather4_2d(vdst + cb * (TNS * 128) + roff, &map_v, it.hk * HDV + cb * 64, y[0], y[1], y[2], y[3],
+                               bar_full + 8 * s);
+            }
+          }
+          ++cnt;
+        }
+        continue;
+      }
       for (int key0 = it.lo * TN; key0 < key_end && ok; key0 += TNS) {
         const int lp0 = key0 / ps;              // first logical page of this stage
         if (paged && (cache_first < 0 || lp0 < cache_first || lp0 + boxes > cache_first + 32)) {
@@ -634,7 +684,8 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
   a.total_work = num_work_slots * kp.hkv * kp.nsplits;
   constexpr int TNS = SM::TNS;
   const bool paged = kp.page_table != nullptr;
-  a.box_rows = (paged && kp.page_size < TNS) ? kp.page_size : TNS;
+  a.gather = paged && (kp.page_size == 1 || kp.page_size == 2 || kp.page_size == 4);
+  a.box_rows = a.gather ? 1 : ((paged && kp.page_size < TNS) ? kp.page_size : TNS);
   const uint64_t rows = paged ? (uint64_t)kp.num_pages * (uint64_t)kp.page_size : (uint64_t)kp.total_k;
   a.kv_total_rows = (int)rows;
   const int kvdt = KV8 ? FA_DT_FP8_E4M3 : (std::is_same<T, __half>::value ? FA_DT_FP16 : FA_DT_BF16);
@@ -661,7 +712,8 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
 }  // namespace dec
 
 // Shapes the decode route takes: head_dim 64, 128 or 192 (values 128), 16-bit queries, a cache of the same type or
-// (head_dim 128) of e4m3 bytes, K/V contiguous or in pages of 16 or 32 keys or whole 64-key TMA boxes.  These are the
+// (head_dim 128) of e4m3 bytes, K/V contiguous or in pages of 1, 2, 4, 8, 16, 32 or a multiple of 64 keys (the small
+// pages through the gather form of the reference's producers, kernels/fa4_blackwell.cu:8042-8062).  These are the
 // head dims of the reference's paged kernel (kernels/fa4_blackwell.cu:9958-9983).
 bool decode_supported(const PlanInput& in) {
   if (in.q_dtype == FA_DT_FP8_E4M3) return false;
@@ -670,7 +722,9 @@ bool decode_supported(const PlanInput& in) {
                      (in.kv_dtype != FA_DT_FP8_E4M3 && ((in.hd == 64 && in.hdv == 64) || (in.hd == 192 && in.hdv == 128)));
   if (!hd_ok) return false;
   const int ps = in.page_size;
-  if (!(ps == 0 || ps == 16 || ps == 32 || ps % 64 == 0)) return false;   // pages divide a 64-row TMA box or are whole boxes
+  // pages of 8, 16 or 32 keys divide a 64-row stage into whole 1024-byte swizzle atoms; multiples of 64 are whole
+  // stages; pages of 1, 2 or 4 keys are gathered four rows at a time
+  if (!(ps == 0 || ps == 1 || ps == 2 || ps == 4 || ps == 8 || ps == 16 || ps == 32 || ps % 64 == 0)) return false;
   return in.hkv > 0 && in.hq % in.hkv == 0 && in.tc_layout_ok;
 }
 

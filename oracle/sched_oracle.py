@@ -94,7 +94,7 @@ def decode_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> bool:
         return False
     if not ((hd, hdv) == (128, 128) or (kv_dtype != DT_FP8 and (hd, hdv) in ((64, 64), (192, 128)))):
         return False
-    if not (page_size in (0, 16, 32) or page_size % 64 == 0):   # contiguous, pages that divide a 64-row TMA box, or whole boxes
+    if not (page_size in (0, 1, 2, 4, 8, 16, 32) or page_size % 64 == 0):   # contiguous, gathered, atoms of a 64-row stage, whole stages
         return False
     return hq % hkv == 0
 

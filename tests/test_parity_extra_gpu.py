@@ -94,6 +94,20 @@ def test_small_pages(page_size, cuda_device):
         _check(p, cuda_device, AUTO, 2e-2)
 
 
+@pytest.mark.parametrize("kv_dtype", [None, "fp8"])
+@pytest.mark.parametrize("page_size", [1, 2, 4, 8])
+def test_decode_route_gathers_small_pages(page_size, kv_dtype, cuda_device):
+    """The streaming decode kernel over pages of 1, 2 and 4 keys (rows gathered four at a time) and of 8 keys, with a
+    permuted page table, leftpad, ragged ends, several query tokens and split-KV."""
+    p = W.make_problem(f"dec_gather_p{page_size}_{kv_dtype}", [(1, 1000), (2, 257), (1, 64), (1, 3), (4, 130)], hq=8,
+                       hkv=2, hd=128, causal=True, page_size=page_size, leftpad=[9, 0, 0, 1, 66], kv_dtype=kv_dtype,
+                       sink=True, seed=55)
+    tol = 6e-2 if kv_dtype else 2e-2
+    _check(p, cuda_device, DEC, tol)
+    _check(p, cuda_device, DEC, tol, num_splits=3)
+    _check(p, cuda_device, AUTO, tol)
+
+
 @pytest.mark.parametrize("page_size", [16, 32, 64, 128, 256])
 @pytest.mark.parametrize("dtype", ["bf16", "fp8"])
 def test_tensor_core_prefill_over_pages(page_size, dtype, cuda_device):
