@@ -24,7 +24,7 @@ TORCH_SO = os.path.join(LIB, "fa_b200_torch.so")
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
-CU_SOURCES = ["fa_capi.cu", "fa_general.cu", "fa_combine.cu", "fa_decode.cu", "fa_prefill_tc.cu"]
+CU_SOURCES = ["fa_capi.cu", "fa_general.cu", "fa_combine.cu", "fa_decode.cu", "fa_prefill_tc.cu", "fa_append.cu"]
 HEADERS = ["fa_internal.h", "fa_sched.h", "ptx.cuh"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
               "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]

@@ -26,7 +26,8 @@ EXPORTS = (
     "fa_b200_fwd_workspace_bytes", "fa_b200_fwd", "fa_b200_num_splits", "fa_b200_scheduler_metadata_len",
     "fa_b200_get_scheduler_metadata", "fa_b200_combine", "fa_b200_check_status", "fa_b200_strerror",
     "fa_b200_last_cuda_error", "fa_b200_version", "fa_b200_sizeof_fwd_params", "fa_b200_sizeof_sched_params",
-    "fa_b200_decode_fwd_static", "fa_b200_combine_strided", "fa_b200_selftest_timeout",
+    "fa_b200_decode_fwd_static", "fa_b200_combine_strided", "fa_b200_selftest_timeout", "fa_b200_append_kv",
+    "fa_b200_sizeof_append_params",
 )
 
 _vp, _i32, _i64, _f32 = C.c_void_p, C.c_int32, C.c_int64, C.c_float
@@ -54,6 +55,20 @@ class FaSchedParams(C.Structure):
         + [(n, _i32) for n in ("batch", "max_seqlen_q", "max_seqlen_k", "hq", "hkv", "hd", "hdv", "qkv_dtype",
                                "page_size", "is_causal", "window_left", "window_right", "has_softcap",
                                "num_splits", "sm_margin")]
+    )
+
+
+class FaAppendParams(C.Structure):
+    _fields_ = (
+        [(n, _vp) for n in ("k_new", "v_new", "k_cache", "v_cache", "q", "q_out", "rotary_cos", "rotary_sin",
+                            "cu_seqlens_k_new", "cu_seqlens_q", "seqused_k", "seqused_k_out", "page_table",
+                            "seqlens_rotary")]
+        + [(n, _i64) for n in ("kn_row_stride", "kn_head_stride", "vn_row_stride", "vn_head_stride", "k_row_stride",
+                               "k_head_stride", "k_page_stride", "v_row_stride", "v_head_stride", "v_page_stride",
+                               "q_row_stride", "q_head_stride", "qo_row_stride", "qo_head_stride")]
+        + [(n, _i32) for n in ("batch", "total_new", "total_q", "hq", "hkv", "hd", "hdv", "page_size",
+                               "page_table_stride", "rotary_dim", "rotary_interleaved", "q_positions_advance",
+                               "q_dtype", "kv_dtype")]
     )
 
 
@@ -92,6 +107,9 @@ def load(build_if_missing: bool = True):
                                             _vp, _vp]
     lib.fa_b200_selftest_timeout.restype = C.c_int
     lib.fa_b200_selftest_timeout.argtypes = [_vp, _i64, _vp]
+    lib.fa_b200_append_kv.restype = C.c_int
+    lib.fa_b200_append_kv.argtypes = [C.POINTER(FaAppendParams), _vp]
+    lib.fa_b200_sizeof_append_params.restype = C.c_size_t
     lib.fa_b200_check_status.restype = C.c_int
     lib.fa_b200_check_status.argtypes = [_vp, _vp, C.POINTER(C.c_uint32)]
     lib.fa_b200_strerror.restype = C.c_char_p
@@ -103,7 +121,8 @@ def load(build_if_missing: bool = True):
     lib.fa_b200_sizeof_fwd_params.restype = C.c_size_t
     lib.fa_b200_sizeof_sched_params.restype = C.c_size_t
     if (lib.fa_b200_sizeof_fwd_params() != C.sizeof(FaFwdParams)
-            or lib.fa_b200_sizeof_sched_params() != C.sizeof(FaSchedParams)):
+            or lib.fa_b200_sizeof_sched_params() != C.sizeof(FaSchedParams)
+            or lib.fa_b200_sizeof_append_params() != C.sizeof(FaAppendParams)):
         raise RuntimeError("ctypes struct layout does not match libfa_b200.so; rebuild the library")
     _lib = lib
     return lib
@@ -316,6 +335,46 @@ def partial_buffer(total_q: int, hq: int, hdv: int, device):
     n_o, per = partial_layout(total_q, hq, hdv)
     buf = torch.empty(per, device=device, dtype=torch.float32)
     return buf, buf[:n_o].view(total_q, hq, hdv), buf[n_o:n_o + hq * total_q].view(hq, total_q)
+
+
+def append_kv(k_new, v_new, k_cache, v_cache, *, page_table, seqused_k, cu_seqlens_k_new, q=None, cu_seqlens_q=None,
+              rotary_cos=None, rotary_sin=None, seqlens_rotary=None, rotary_interleaved=True,
+              q_positions_advance=True):
+    """Appends k_new / v_new (total_new, hkv, d) to the paged cache IN PLACE through `fa_b200_append_kv` and, with a
+    rotary table, rotates them and returns a rotated copy of q.  Returns (q_rotated or q, seqused_k after the append)."""
+    lib = load()
+    p = FaAppendParams()
+    p.k_new, p.v_new, p.k_cache, p.v_cache = k_new.data_ptr(), v_new.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr()
+    p.kn_row_stride, p.kn_head_stride = k_new.stride(0), k_new.stride(1)
+    p.vn_row_stride, p.vn_head_stride = v_new.stride(0), v_new.stride(1)
+    p.k_page_stride, p.k_row_stride, p.k_head_stride = k_cache.stride(0), k_cache.stride(1), k_cache.stride(2)
+    p.v_page_stride, p.v_row_stride, p.v_head_stride = v_cache.stride(0), v_cache.stride(1), v_cache.stride(2)
+    p.total_new, p.hkv, p.hd = k_new.shape
+    p.hdv = v_new.shape[2]
+    p.page_size = k_cache.shape[1]
+    p.page_table, p.page_table_stride = page_table.data_ptr(), page_table.stride(0)
+    p.batch = seqused_k.numel()
+    seq_out = torch.empty_like(seqused_k)
+    p.seqused_k, p.seqused_k_out, p.cu_seqlens_k_new = seqused_k.data_ptr(), seq_out.data_ptr(), cu_seqlens_k_new.data_ptr()
+    p.kv_dtype = dtype_code(k_cache.dtype)
+    q_out = q
+    if rotary_cos is not None:
+        q_out = torch.empty(q.shape, device=q.device, dtype=q.dtype)
+        p.q, p.q_out, p.cu_seqlens_q = q.data_ptr(), q_out.data_ptr(), cu_seqlens_q.data_ptr()
+        p.total_q, p.hq, _ = q.shape
+        p.q_row_stride, p.q_head_stride = q.stride(0), q.stride(1)
+        p.qo_row_stride, p.qo_head_stride = q_out.stride(0), q_out.stride(1)
+        p.rotary_cos, p.rotary_sin = rotary_cos.data_ptr(), rotary_sin.data_ptr()
+        p.rotary_dim = 2 * rotary_cos.shape[1]
+        p.seqlens_rotary = _ptr(seqlens_rotary)
+        p.rotary_interleaved, p.q_positions_advance = int(bool(rotary_interleaved)), int(bool(q_positions_advance))
+        p.q_dtype = dtype_code(q.dtype)
+    else:
+        p.q_dtype = FA_DT_BF16 if k_cache.dtype == torch.float8_e4m3fn else dtype_code(k_new.dtype)
+    rc = lib.fa_b200_append_kv(C.byref(p), _stream())
+    if rc != FA_OK:
+        raise FaError(rc, "append_kv")
+    return q_out, seq_out
 
 
 def selftest_timeout(device, max_cycles: int = 200_000) -> torch.Tensor:

@@ -15,6 +15,7 @@ namespace fa {
 
 int launch_sched(const FaSchedParams& sp, const Plan& pl, int32_t* out_dev, int32_t* zero_words, cudaStream_t stream);
 int launch_selftest_timeout(DeviceStatus* status, long long max_cycles, cudaStream_t stream);
+int launch_append_kv(const FaAppendParams& p, int num_sms, cudaStream_t stream);
 int launch_combine_strided(const float* o_part, const float* lse_part, int64_t o_split_stride, int64_t lse_split_stride,
                            int nsplits, int total_q, int hq, int hdv, const float* s_aux, void* out,
                            int64_t o_row_stride, int64_t o_head_stride, int out_dtype, float* lse, cudaStream_t stream);
@@ -421,6 +422,36 @@ int fa_b200_combine_strided(const float* o_part, const float* lse_part, int64_t 
                                                 hq, hdv, s_aux, out, o_row_stride, o_head_stride, out_dtype, lse,
                                                 (cudaStream_t)stream),
                          "combine kernel");
+}
+
+size_t fa_b200_sizeof_append_params(void) { return sizeof(FaAppendParams); }
+
+int fa_b200_append_kv(const FaAppendParams* p, fa_stream_t stream) {
+  if (!p || !p->k_new || !p->v_new || !p->k_cache || !p->v_cache || !p->cu_seqlens_k_new || !p->seqused_k ||
+      !p->seqused_k_out || !p->page_table || p->seqused_k_out == p->seqused_k)
+    return FA_ERR_BAD_ARG;
+  if (p->batch < 0 || p->total_new < 0 || p->hkv <= 0 || p->page_size <= 0) return FA_ERR_BAD_ARG;
+  const bool kv8 = p->kv_dtype == FA_DT_FP8_E4M3;
+  if (p->kv_dtype < 0 || p->kv_dtype > 2 || p->q_dtype < 0 || p->q_dtype > 1) return FA_ERR_UNSUPPORTED;
+  const int esz = kv8 ? 1 : 2, epc = 16 / esz;   // elements per 16-byte chunk
+  if (p->hd % epc || p->hdv % epc) return FA_ERR_UNSUPPORTED;
+  const int64_t st[] = {p->kn_row_stride, p->kn_head_stride, p->vn_row_stride, p->vn_head_stride, p->k_row_stride,
+                        p->k_head_stride, p->k_page_stride, p->v_row_stride, p->v_head_stride, p->v_page_stride};
+  for (int64_t s : st) if (s % epc) return FA_ERR_UNSUPPORTED;
+  const uintptr_t ptrs[] = {(uintptr_t)p->k_new, (uintptr_t)p->v_new, (uintptr_t)p->k_cache, (uintptr_t)p->v_cache};
+  for (uintptr_t a : ptrs) if (a % 16) return FA_ERR_UNSUPPORTED;
+  if (p->rotary_cos) {
+    if (!p->rotary_sin || !p->q || !p->q_out || !p->cu_seqlens_q || p->q_out == p->q) return FA_ERR_BAD_ARG;
+    if (kv8 || p->kv_dtype != p->q_dtype) return FA_ERR_UNSUPPORTED;       // keys are rotated in the query type
+    if (p->rotary_dim <= 0 || p->rotary_dim % 16 || p->rotary_dim > p->hd || p->hd % 8) return FA_ERR_UNSUPPORTED;
+    if (p->q_row_stride % 8 || p->q_head_stride % 8 || p->qo_row_stride % 8 || p->qo_head_stride % 8 ||
+        ((uintptr_t)p->q % 16) || ((uintptr_t)p->q_out % 16) || ((uintptr_t)p->rotary_cos % 16) || ((uintptr_t)p->rotary_sin % 16))
+      return FA_ERR_UNSUPPORTED;
+  }
+  const DevInfo* di = device_info();
+  if (!di || !di->ok) return FA_ERR_NO_DEVICE;
+  if (p->batch == 0) return FA_OK;
+  return note_cuda_error(launch_append_kv(*p, di->sms, (cudaStream_t)stream), "append kernel");
 }
 
 int fa_b200_selftest_timeout(void* workspace, int64_t max_cycles, fa_stream_t stream_) {

@@ -121,14 +121,27 @@ std::vector<at::Tensor> mha_fwd(
   TORCH_CHECK(q.is_cuda() && k.is_cuda() && v.is_cuda(), "fa_b200: q, k, v must be CUDA tensors");
   const at::cuda::OptionalCUDAGuard guard(q.device());
   TORCH_CHECK(q.dim() == 3, "fa_b200: unsupported config (q must be (total_q, hq, hd))");
-  const bool paged = page_table.has_value();
+  TORCH_CHECK(cu_seqlens_q.has_value(), "fa_b200: unsupported config (cu_seqlens_q is required)");
+  TORCH_CHECK(!q_v.has_value() && !seqused_q.has_value() && cp_world_size <= 1,
+              "fa_b200: unsupported config (q_v / seqused_q / context-parallel)");
+  TORCH_CHECK(k_new.has_value() == v_new.has_value(), "fa_b200: unsupported config (k_new and v_new come together)");
+  TORCH_CHECK(rotary_cos.has_value() == rotary_sin.has_value() && (!rotary_cos.has_value() || k_new.has_value()),
+              "fa_b200: unsupported config (rotary_cos and rotary_sin come together, and only with k_new / v_new)");
+  // A cache laid out (batch_cache, seqlen_cache, hkv, d) without a page table is a paged cache with one page per row
+  // of the batch: page b (or kv_batch_idx[b]) belongs to sequence b.
+  bool paged = page_table.has_value();
+  if (!paged && k.dim() == 4) {
+    TORCH_CHECK(seqused_k.has_value(), "fa_b200: unsupported config (a (batch, seqlen, heads, dim) cache needs seqused_k)");
+    const int64_t nb = cu_seqlens_q->numel() - 1;
+    page_table = kv_batch_idx.has_value()
+                     ? kv_batch_idx->to(at::kInt).reshape({nb, 1}).contiguous()
+                     : at::arange(nb, seqused_k->options().dtype(at::kInt)).reshape({nb, 1});
+    paged = true;
+  } else {
+    TORCH_CHECK(!kv_batch_idx.has_value(), "fa_b200: unsupported config (kv_batch_idx with a paged or packed cache)");
+  }
   TORCH_CHECK(k.dim() == (paged ? 4 : 3) && v.dim() == k.dim(),
               "fa_b200: unsupported config (k/v rank does not match paged=", paged, ")");
-  TORCH_CHECK(!k_new.has_value() && !v_new.has_value() && !q_v.has_value() && !rotary_cos.has_value() &&
-                  !rotary_sin.has_value() && !kv_batch_idx.has_value() && !seqused_q.has_value() &&
-                  !cu_seqlens_k_new.has_value() && cp_world_size <= 1,
-              "fa_b200: unsupported config (k_new/v_new/q_v/rotary/kv_batch_idx/seqused_q/context-parallel)");
-  TORCH_CHECK(cu_seqlens_q.has_value(), "fa_b200: unsupported config (cu_seqlens_q is required)");
   TORCH_CHECK(q.stride(2) == 1 && k.stride(-1) == 1 && v.stride(-1) == 1,
               "fa_b200: unsupported config (the last dim of q, k, v must be contiguous)");
 
@@ -182,6 +195,69 @@ std::vector<at::Tensor> mha_fwd(
   p.max_seqlen_k = max_seqlen_k.has_value() ? (int)*max_seqlen_k
                    : paged               ? (int)(page_table->size(1) * k.size(1))
                                          : (int)k.size(0);
+
+  // ---- k_new / v_new: append to the cache in place (and rotate) before the attention call ----
+  at::Tensor q_rot, seq_after, cu_new, kn, vn, rcos, rsin;
+  if (k_new.has_value()) {
+    TORCH_CHECK(paged && seqused_k.has_value(), "fa_b200: unsupported config (k_new / v_new need a paged or (batch, seqlen) cache and seqused_k)");
+    TORCH_CHECK(!leftpad_k.has_value(), "fa_b200: unsupported config (k_new / v_new with leftpad_k)");
+    kn = *k_new; vn = *v_new;
+    TORCH_CHECK(kn.scalar_type() == k.scalar_type() && vn.scalar_type() == v.scalar_type() && kn.is_cuda() && vn.is_cuda(),
+                "fa_b200: unsupported config (k_new / v_new must have the cache's dtype)");
+    int64_t max_new = 0;
+    if (kn.dim() == 4) {   // (batch, seqlen_new, hkv, d): every sequence gets seqlen_new keys
+      const int64_t s_new = kn.size(1);
+      TORCH_CHECK(kn.size(0) == p.batch && vn.dim() == 4, "fa_b200: unsupported config (k_new batch size)");
+      cu_new = at::arange(0, (p.batch + 1) * s_new, s_new, seqused_k->options().dtype(at::kInt));
+      kn = kn.reshape({p.batch * s_new, kn.size(2), kn.size(3)});
+      vn = vn.reshape({p.batch * s_new, vn.size(2), vn.size(3)});
+      max_new = s_new;
+    } else {
+      TORCH_CHECK(kn.dim() == 3 && vn.dim() == 3 && cu_seqlens_k_new.has_value(),
+                  "fa_b200: unsupported config (packed k_new needs cu_seqlens_k_new)");
+      cu_new = *cu_seqlens_k_new;
+      max_new = kn.size(0);
+    }
+    TORCH_CHECK(kn.stride(2) == 1 && vn.stride(2) == 1 && kn.size(1) == p.hkv && kn.size(2) == p.hd && vn.size(2) == p.hdv,
+                "fa_b200: unsupported config (k_new / v_new shape or layout)");
+    std::optional<at::Tensor> cu_new_o(cu_new);
+    FaAppendParams ap{};
+    ap.k_new = kn.data_ptr(); ap.v_new = vn.data_ptr(); ap.k_cache = k.data_ptr(); ap.v_cache = v.data_ptr();
+    ap.kn_row_stride = kn.stride(0); ap.kn_head_stride = kn.stride(1);
+    ap.vn_row_stride = vn.stride(0); ap.vn_head_stride = vn.stride(1);
+    ap.k_page_stride = p.k_page_stride; ap.k_row_stride = p.k_row_stride; ap.k_head_stride = p.k_head_stride;
+    ap.v_page_stride = p.v_page_stride; ap.v_row_stride = p.v_row_stride; ap.v_head_stride = p.v_head_stride;
+    ap.cu_seqlens_k_new = i32(cu_new_o, "cu_seqlens_k_new");
+    ap.cu_seqlens_q = p.cu_seqlens_q;
+    ap.seqused_k = p.seqused_k;
+    seq_after = at::empty_like(*seqused_k);
+    ap.seqused_k_out = seq_after.data_ptr<int32_t>();
+    ap.page_table = p.page_table; ap.page_table_stride = p.page_table_stride; ap.page_size = p.page_size;
+    ap.batch = p.batch; ap.total_new = (int)kn.size(0); ap.total_q = p.total_q;
+    ap.hq = p.hq; ap.hkv = p.hkv; ap.hd = p.hd; ap.hdv = p.hdv;
+    ap.kv_dtype = p.kv_dtype; ap.q_dtype = p.q_dtype == FA_DT_FP16 ? FA_DT_FP16 : FA_DT_BF16;
+    if (rotary_cos.has_value()) {
+      TORCH_CHECK(p.q_dtype != FA_DT_FP8_E4M3, "fa_b200: unsupported config (rotary with e4m3 queries)");
+      rcos = rotary_cos->to(q.scalar_type()).contiguous();
+      rsin = rotary_sin->to(q.scalar_type()).contiguous();
+      TORCH_CHECK(rcos.dim() == 2 && rsin.sizes() == rcos.sizes(), "fa_b200: unsupported config (rotary tables must be (seqlen_ro, rotary_dim/2))");
+      q_rot = at::empty(q.sizes(), q.options());
+      ap.q = q.data_ptr(); ap.q_out = q_rot.data_ptr();
+      ap.q_row_stride = q.stride(0); ap.q_head_stride = q.stride(1);
+      ap.qo_row_stride = q_rot.stride(0); ap.qo_head_stride = q_rot.stride(1);
+      ap.rotary_cos = rcos.data_ptr(); ap.rotary_sin = rsin.data_ptr();
+      ap.rotary_dim = 2 * (int)rcos.size(1);
+      ap.seqlens_rotary = i32(seqlens_rotary, "seqlens_rotary");
+      ap.rotary_interleaved = is_rotary_interleaved ? 1 : 0;
+      ap.q_positions_advance = (is_causal || window_size_left >= 0 || window_size_right >= 0) ? 1 : 0;
+    }
+    const int arc = fa_b200_append_kv(&ap, (fa_stream_t)at::cuda::getCurrentCUDAStream().stream());
+    TORCH_CHECK(arc != FA_ERR_UNSUPPORTED, "fa_b200: unsupported config (k_new / v_new / rotary shapes or alignment)");
+    check_rc(arc, "append_kv");
+    p.seqused_k = seq_after.data_ptr<int32_t>();
+    if (q_rot.defined()) { p.q = q_rot.data_ptr(); p.q_row_stride = q_rot.stride(0); p.q_head_stride = q_rot.stride(1); }
+    p.max_seqlen_k = (int)std::min<int64_t>((int64_t)p.max_seqlen_k + max_new, page_table->size(1) * (int64_t)p.page_size);
+  }
 
   // fp8 descales: (batch, hkv) float tables or one-element tensors, materialised as (batch, hkv) fp32
   at::Tensor qd, kd, vd;

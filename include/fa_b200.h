@@ -151,6 +151,43 @@ int fa_b200_combine_strided(const float* o_part, const float* lse_part, int64_t 
                             const float* s_aux, void* out, int64_t o_row_stride, int64_t o_head_stride,
                             int32_t out_dtype, float* lse, fa_stream_t stream);
 
+/* Appends the new keys / values of this step to a paged cache, in place, and applies the rotary position embedding to
+ * them and to the queries: the step in front of the attention call when the op is given `k_new` / `v_new` /
+ * `rotary_cos` / `rotary_sin`.  Those arguments exist in the op's schema (kernels/fa4_blackwell.cu:10188-10196), but the
+ * reference pins them to None (bench/scenarios.py:915-921) and has no kernel for them; the behaviour here is the op's
+ * documented one: new key i of sequence b lands at key index seqused_k[b] + i and is rotated at position r_b + i,
+ * r_b = seqlens_rotary[b] if given else seqused_k[b]; query i is rotated at r_b + i when q_positions_advance is set
+ * (causal or windowed attention) and at r_b otherwise; `rotary_interleaved` pairs dimensions (2j, 2j+1), else
+ * (j, j + rotary_dim/2); dimensions >= rotary_dim pass through.  All arithmetic is fp32 with separately rounded
+ * products and sums, results rounded to the element type.  Strides in ELEMENTS. */
+typedef struct FaAppendParams {
+  const void* k_new;             /* (total_new, hkv, hd), element type kv_dtype */
+  const void* v_new;             /* (total_new, hkv, hdv) */
+  void* k_cache;                 /* (num_pages, page_size, hkv, hd), written in place */
+  void* v_cache;                 /* (num_pages, page_size, hkv, hdv) */
+  const void* q;                 /* (total_q, hq, hd), element type q_dtype; read only when a rotary table is given */
+  void* q_out;                   /* (total_q, hq, hd) rotated copy of q (must not alias q); NULL without rotary */
+  const void* rotary_cos;        /* (seqlen_ro, rotary_dim/2) of q_dtype, or NULL: no rotation */
+  const void* rotary_sin;
+  const int32_t* cu_seqlens_k_new; /* (batch+1) */
+  const int32_t* cu_seqlens_q;     /* (batch+1); needed with rotary */
+  const int32_t* seqused_k;        /* (batch) keys in the cache before the call */
+  int32_t* seqused_k_out;          /* (batch) keys after it: seqused_k + new keys (must not alias seqused_k) */
+  const int32_t* page_table;       /* (batch, page_table_stride) */
+  const int32_t* seqlens_rotary;   /* (batch) or NULL */
+  int64_t kn_row_stride, kn_head_stride, vn_row_stride, vn_head_stride;
+  int64_t k_row_stride, k_head_stride, k_page_stride, v_row_stride, v_head_stride, v_page_stride;
+  int64_t q_row_stride, q_head_stride, qo_row_stride, qo_head_stride;
+  int32_t batch, total_new, total_q, hq, hkv, hd, hdv;
+  int32_t page_size, page_table_stride;
+  int32_t rotary_dim;              /* multiple of 16, <= hd */
+  int32_t rotary_interleaved, q_positions_advance;
+  int32_t q_dtype, kv_dtype;       /* FA_DT_*; rotary needs 16-bit q and k_new of the same type; an e4m3 cache takes
+                                    * e4m3 k_new / v_new without rotation of the keys */
+} FaAppendParams;
+int fa_b200_append_kv(const FaAppendParams* p, fa_stream_t stream);
+size_t fa_b200_sizeof_append_params(void);
+
 /* Reads the device status word of a workspace after synchronising `stream` (the only entry point that
  * synchronises). Returns FA_OK, FA_ERR_DEVICE_TIMEOUT with *detail = (role<<24 | block) of the first
  * wait that gave up, or FA_ERR_BAD_METADATA when a kernel refused the scheduler metadata. The reference has
