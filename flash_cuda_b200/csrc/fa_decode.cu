@@ -104,8 +104,8 @@ __device__ __forceinline__ WorkItem decode_work(const KParams& p, int w) {
 }
 
 // T = MMA element type (bf16 / fp16); KV8 = the cache holds e4m3 bytes.
-template <typename T, bool KV8, int NST, int HD, int HDV>
-__global__ void __launch_bounds__((ncons_for(KV8 ? 1 : 2) + 1) * 32, ctas_per_sm(KV8 ? 1 : 2))
+template <typename T, bool KV8, int NST, int HD, int HDV, int CPS>
+__global__ void __launch_bounds__((ncons_for(KV8 ? 1 : 2) + 1) * 32, CPS)
 fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
   constexpr int ESZ = KV8 ? 1 : 2;
   static_assert(!KV8 || (HD == 128 && HDV == 128), "an e4m3 cache row must fill one 128-byte swizzle row");
@@ -148,7 +148,7 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
     uint32_t cnt = 0;
     bool ok = true;
     const bool paged = p.page_table != nullptr;
-    const int ps = paged ? p.page_size : TNS;   // contiguous K/V: "pages" of one stage, at rows k0 + key
+    const int ps = paged ? p.page_size : TNS;   // contiguous K/V: "pages" of one stage, at rows k0 + key (page_shift is -1 then)
     const int boxes = TNS / a.box_rows;         // TMA boxes per stage and 128-byte column block
     // the list's header must describe this call before any entry is read
     int total_work = a.total_work;
@@ -190,15 +190,15 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         // 128-byte column block of K and V.  Keys beyond the sequence fetch pool row 0 and are masked by the consumers.
         const int32_t* pt = p.page_table + (int64_t)it.b * p.page_table_stride;
         for (int key0 = it.lo * TN; key0 < key_end && ok; key0 += TNS) {
+          // lanes 0..15 copy K, lanes 16..31 copy V; lane (g = lane & 15) owns keys 4g .. 4g+3 of the stage
           int y[4] = {0, 0, 0, 0};
-          if (lane < TNS / 4) {
+          const int grp = lane & 15;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int kk = key0 + 4 * lane + j;
-              if (kk < it.seqlen_k && kk < key_end) {
-                const int lp = kk / ps;
-                y[j] = pt[lp] * ps + (kk - lp * ps);
-              }
+          for (int j = 0; j < 4; ++j) {
+            const int kk = key0 + 4 * grp + j;
+            if (kk < it.seqlen_k && kk < key_end) {
+              const int lp = kk >> p.page_shift;          // gather mode: the page size is 1, 2 or 4
+              y[j] = (pt[lp] << p.page_shift) + (kk - (lp << p.page_shift));
             }
           }
           const uint32_t s = cnt % NST;
@@ -212,22 +212,16 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
             s_info[4 * s] = w; s_info[4 * s + 1] = key0; s_info[4 * s + 2] = flags;
             mbar_expect_tx(bar_full + 8 * s, SM::kStage);
           }
-          __syncwarp();
-          if (lane < TNS / 4) {
-            const uint32_t roff = (uint32_t)(4 * lane) * 128u;
-            if (KV8) {
-              tma_gather4_2d(kdst + roff, &map_k, it.hk * HD, y[0], y[1], y[2], y[3], bar_full + 8 * s);
-              tma_gather4_2d(vdst + roff, &map_v, it.hk * HDV, y[0], y[1], y[2], y[3], bar_full + 8 * s);
-            } else {
-#pragma unroll
-              for (int cb = 0; cb < HD / 64; ++cb)
-                tma_gather4_2d(kdst + cb * (TNS * 128) + roff, &map_k, it.hk * HD + cb * 64, y[0], y[1], y[2], y[3],
-                               bar_full + 8 * s);
-#pragma unroll
-              for (int cb = 0; cb < HDV / 64; ++cb)
-                tma_gather4_2d(vdst + cb * (TNS * 128) + roff, &map_v, it.hk * HDV + cb * 64, y[0], y[1], y[2], y[3],
-                               bar_full + 8 * s);
-            }
+          {
+            const uint32_t roff = (uint32_t)(4 * grp) * 128u;
+            const bool is_v = lane >= 16;
+            const uint32_t dst = (is_v ? vdst : kdst) + roff;
+            const CUtensorMap* map = is_v ? &map_v : &map_k;
+            const int x0 = it.hk * (is_v ? HDV : HD);
+            constexpr int EPB = KV8 ? 128 : 64;           // elements per 128-byte column block
+            const int ncb = (is_v ? HDV : HD) / EPB;
+            for (int cb = 0; cb < ncb; ++cb)
+              tma_gather4_2d(dst + cb * (TNS * 128), map, x0 + cb * EPB, y[0], y[1], y[2], y[3], bar_full + 8 * s);
           }
           ++cnt;
         }
@@ -251,25 +245,23 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
           s_info[4 * s] = w; s_info[4 * s + 1] = key0; s_info[4 * s + 2] = flags;
           mbar_expect_tx(bar_full + 8 * s, SM::kStage);
         }
-        for (int j = 0; j < boxes; ++j) {
+        // one copy per (box, 128-byte column block, K or V); the lanes share them out
+        constexpr int EPB = KV8 ? 128 : 64;              // elements per 128-byte column block
+        constexpr int KCB = HD / EPB, VCB = HDV / EPB, OPB = KCB + VCB;
+        const int nops = boxes * OPB;
+        for (int o0 = 0; o0 < nops; o0 += 32) {
+          const int o = o0 + lane;
+          const bool act = o < nops;
+          const int j = act ? o / OPB : 0, c = o - j * OPB;
           const int kk = key0 + j * a.box_rows;
-          const int lp = kk / ps;
-          const int pid = paged ? __shfl_sync(0xffffffffu, cache_id, lp - cache_first) : 0;
-          if (lane == 0) {
+          const int lp = p.page_shift >= 0 ? (kk >> p.page_shift) : kk / ps;
+          const int pid = paged ? __shfl_sync(0xffffffffu, cache_id, (lp - cache_first) & 31) : 0;
+          if (act) {
             int y = a.kv_total_rows;                 // out of range: TMA fills zeros
             if (kk < it.seqlen_k && kk < key_end && pid >= 0) y = paged ? pid * ps + (kk - lp * ps) : it.k0 + kk;
             const uint32_t roff = (uint32_t)(j * a.box_rows) * 128u;
-            if (KV8) {
-              tma_load_2d(kdst + roff, &map_k, it.hk * HD, y, bar_full + 8 * s);
-              tma_load_2d(vdst + roff, &map_v, it.hk * HDV, y, bar_full + 8 * s);
-            } else {
-#pragma unroll
-              for (int cb = 0; cb < HD / 64; ++cb)
-                tma_load_2d(kdst + cb * (TNS * 128) + roff, &map_k, it.hk * HD + cb * 64, y, bar_full + 8 * s);
-#pragma unroll
-              for (int cb = 0; cb < HDV / 64; ++cb)
-                tma_load_2d(vdst + cb * (TNS * 128) + roff, &map_v, it.hk * HDV + cb * 64, y, bar_full + 8 * s);
-            }
+            if (c < KCB) tma_load_2d(kdst + c * (TNS * 128) + roff, &map_k, it.hk * HD + c * EPB, y, bar_full + 8 * s);
+            else tma_load_2d(vdst + (c - KCB) * (TNS * 128) + roff, &map_v, it.hk * HDV + (c - KCB) * EPB, y, bar_full + 8 * s);
           }
         }
         ++cnt;
@@ -676,7 +668,7 @@ static bool make_map(CUtensorMap* m, const void* ptr, int dtype, uint64_t rows, 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename T, bool KV8, int NST, int HD, int HDV>
+template <typename T, bool KV8, int NST, int HD, int HDV, int CPS = ctas_per_sm(KV8 ? 1 : 2)>
 static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaStream_t stream) {
   using SM = Smem<KV8 ? 1 : 2, NST, HD, HDV>;
   DecArgs a;
@@ -692,7 +684,7 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
   CUtensorMap mk, mv;
   if (!make_map(&mk, kp.k, kvdt, rows, (uint64_t)kp.hkv * HD, (uint64_t)kp.k_row_stride, a.box_rows)) return -1;
   if (!make_map(&mv, kp.v, kvdt, rows, (uint64_t)kp.hkv * HDV, (uint64_t)kp.v_row_stride, a.box_rows)) return -1;
-  auto kern = fwd_decode_kernel<T, KV8, NST, HD, HDV>;
+  auto kern = fwd_decode_kernel<T, KV8, NST, HD, HDV, CPS>;
   const int smem = SM::kBytes + 1024;
   static std::atomic<unsigned long long> attr_done{0};   // one bit per device
   int dev = 0;
@@ -702,7 +694,7 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
     if (e != cudaSuccess) return (int)e;
     if (dev >= 0 && dev < 64) attr_done.fetch_or(1ull << dev, std::memory_order_release);
   }
-  const int ctas = pl.num_sms * ctas_per_sm(KV8 ? 1 : 2);
+  const int ctas = pl.num_sms * CPS;
   int grid = a.total_work < ctas ? a.total_work : ctas;
   if (grid <= 0) return 0;
   kern<<<grid, (SM::NC + 1) * 32, smem, stream>>>(a, mk, mv);
@@ -731,7 +723,7 @@ bool decode_supported(const PlanInput& in) {
 template <typename T>
 static int launch_decode_t(const KParams& kp, const Plan& pl, int slots, cudaStream_t stream) {
   if (kp.kv_fp8) return dec::launch_t<T, true, 4, 128, 128>(kp, pl, slots, stream);
-  if (kp.hd == 64) return dec::launch_t<T, false, 10, 64, 64>(kp, pl, slots, stream);
+  if (kp.hd == 64) return dec::launch_t<T, false, 5, 64, 64, 2>(kp, pl, slots, stream);   // 16 KB stages: two CTAs per SM
   if (kp.hd == 192) return dec::launch_t<T, false, 4, 192, 128>(kp, pl, slots, stream);
   return dec::launch_t<T, false, 5, 128, 128>(kp, pl, slots, stream);
 }
