@@ -166,6 +166,113 @@ def run_reference(args) -> None:
 
 
 # ----------------------------------------------------------------------------------------------------
+# optional arm: the reference's own sm_100a kernel beside ours, same tensors, same loop (one GPU)
+# ----------------------------------------------------------------------------------------------------
+AB_SHAPES = ("c2", "c1", "h16_s4k", "h16_s8k", "c4")
+
+
+def _ab_problem(name):
+    from flash_cuda_b200 import workloads as W
+    if name == "c2":
+        return W.causal_gqa_prefill()
+    if name == "c1":
+        return W.dense_noncausal()
+    if name == "h16_s4k":
+        return W.make_problem("dense_c_d128_s4k", [(4096, 4096)] * 4, hq=16, hkv=16, hd=128, causal=True)
+    if name == "h16_s8k":
+        return W.make_problem("dense_c_d128_s8k", [(8192, 8192)] * 2, hq=16, hkv=16, hd=128, causal=True)
+    if name == "c4":
+        p = W.paged_decode()
+        p.leftpad_k = None      # the reference's kernel reads only leftpad_k[0] (kernels/fa4_blackwell.cu:10126-10127)
+        return p
+    raise SystemExit(f"unknown A/B shape {name!r}; choose from {AB_SHAPES}")
+
+
+def run_ab_one(name: str) -> None:
+    """One shape, in a process of its own: ours and the reference's kernel on the same device tensors, alternating
+    over 4 rotating input copies, median of 20 CUDA-event timings each; numerics of one against the other."""
+    from dataclasses import replace
+    from flash_cuda_b200 import ops
+    so = os.path.join(ROOT, "oracle", "_ref", "fa4_ref.so")
+    if not os.path.isfile(so):
+        print(json.dumps({"shape": name, "unavailable": "oracle/_ref/fa4_ref.so is not built (python oracle/build_ref.py)"}))
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    ops.load(build_if_missing=False)
+    torch.ops.load_library(so)
+    ref = torch.ops.fa4_ref.fwd
+    p = _ab_problem(name)
+    fl, by = p.flops(), p.kv_bytes()
+    p0 = p.to(dev)
+    R = 4 if name != "c4" else 1       # the decode pool (8.5 GB) is larger than L2 by itself
+    ps = [p0] + [replace(p0, q=p0.q.clone(), k=p0.k.clone(), v=p0.v.clone()) for _ in range(R - 1)]
+    kws = [x.capi_kw() for x in ps]
+
+    def ours(i):
+        x = ps[i % R]
+        return ops.call_fwd(x.q, x.k, x.v, **kws[i % R])
+
+    def theirs(i):
+        x = ps[i % R]
+        return ref(x.q, x.k, x.v, None, None, None, None, x.cu_seqlens_q, x.cu_seqlens_k, None, None, x.seqused_k,
+                   x.max_seqlen_q, x.max_seqlen_k, x.page_table, None, x.leftpad_k, None, None, None, None, None, None,
+                   x.softmax_scale, x.causal, x.window_left, x.window_right, x.softcap, True, None, 0, None, 0,
+                   x.s_aux, 1, 0, None)
+
+    def med(fn, n=20, warm=5):
+        for i in range(warm):
+            fn(i)
+        torch.cuda.synchronize()
+        ts = []
+        for i in range(n):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn(i)
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    o1, l1 = ours(0)
+    r = theirs(0)
+    torch.cuda.synchronize()
+    fin = torch.isfinite(l1)
+    t_o, t_r = med(ours), med(theirs)
+    t_o2, t_r2 = med(ours), med(theirs)          # second pass: the order of the two does not decide the result
+    t_o, t_r = min(t_o, t_o2), min(t_r, t_r2)
+    print(json.dumps({"shape": name, "ours_ms": t_o, "reference_kernel_ms": t_r, "speedup": t_r / t_o,
+                      "ours_TFLOPs": fl / t_o / 1e9, "reference_TFLOPs": fl / t_r / 1e9,
+                      "ours_GBs": by / t_o / 1e6, "reference_GBs": by / t_r / 1e6,
+                      "max_abs_dout": (o1.float() - r[0].float()).abs().max().item(),
+                      "max_abs_dlse": (l1[fin] - r[1][fin]).abs().max().item()}))
+
+
+def run_ab(args) -> None:
+    """`--impl reference-kernel`: the reference's own `kernels/fa4_blackwell.cu` (built by oracle/build_ref.py into
+    oracle/_ref/fa4_ref.so, never on the product path) against ours, shape by shape, each in a child process with a
+    wall-clock limit (the reference's device waits are unbounded).  Shapes the reference cannot run are left out: the
+    varlen + softcap configuration (its kernel for it has a recorded hang class, bench/scenarios.py:630-638), e4m3
+    (unsupported there) and the long-context configuration (its launch asks for more shared memory than the GPU has)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    shapes = [x for x in args.ab_shapes.split(",") if x]
+    rows = []
+    for name in shapes:
+        try:
+            r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-kernel", "--ab-one", name],
+                               stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=args.ab_timeout)
+            line = [ln for ln in r.stdout.strip().splitlines() if ln.startswith("{")]
+            rows.append(json.loads(line[-1]) if line else {"shape": name, "error": (r.stderr or r.stdout)[-400:]})
+        except subprocess.TimeoutExpired:
+            rows.append({"shape": name, "error": f"no result within {args.ab_timeout} s; child process ended"})
+            break      # do not go on after a stall
+    print(json.dumps({"impl": "reference-kernel", "n_gpus": 1, "rows": rows,
+                      "method": "same device tensors, 4 rotating input copies, median of 20 CUDA-event timings, best of two passes"}))
+
+
+# ----------------------------------------------------------------------------------------------------
 # GPU arm
 # ----------------------------------------------------------------------------------------------------
 def _time_steps(fn, steps, dist, world):
@@ -180,12 +287,21 @@ def _time_steps(fn, steps, dist, world):
     b.record()
     torch.cuda.synchronize()
     ms = a.elapsed_time(b) / steps
+    _time_steps.last_min = ms
     if world > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        t = torch.tensor([ms, -ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.barrier()
-        ms = float(t.item())
+        ms, _time_steps.last_min = float(t[0].item()), -float(t[1].item())
     return ms
+
+
+def _build_record():
+    from flash_cuda_b200 import build as B
+    try:
+        return B.build_record()
+    except Exception as e:
+        return {"error": repr(e)}
 
 
 def _tensor_bytes(*ts):
@@ -217,6 +333,26 @@ def _tensor_roofline(tflops, peaks, dtype="bf16", sustained=False):
         src += ", fp8 peak derived as 2 x bf16"
     return {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
             "peak_source": src}
+
+
+def run_decode_only(args) -> None:
+    """`--decode-only`: the two decode legs alone on one GPU, for profiler captures on a small pool."""
+    from flash_cuda_b200 import capi, ops, workloads as W
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    ops.load(build_if_missing=False)
+    res = {}
+    for kv_dtype in ("bf16", "fp8"):
+        dp = W.paged_decode_on_device(dev, seed=0, kv_dtype=kv_dtype, B=args.decode_batch, ctx_hi=args.decode_ctx_max)
+        dout = torch.empty(dp.q.shape[0], dp.q.shape[1], dp.v.shape[-1], device=dev, dtype=torch.bfloat16)
+        kw = dp.capi_kw()
+        for _ in range(max(args.warmup, 3)):
+            ops.call_fwd(dp.q, dp.k, dp.v, out=dout, **kw)
+        ms = _time_steps(lambda i: ops.call_fwd(dp.q, dp.k, dp.v, out=dout, **kw), args.steps, None, 1)
+        res[kv_dtype] = {"ms_per_step": ms, "GB/s": dp.kv_bytes() / (ms * 1e-3) / 1e9, "kv_bytes": dp.kv_bytes()}
+        del dp, dout
+        torch.cuda.empty_cache()
+    print(json.dumps({"decode_only": res, "batch": args.decode_batch, "ctx_max": args.decode_ctx_max, "steps": args.steps}))
 
 
 def run_ours(args) -> None:
@@ -357,7 +493,8 @@ def run_ours(args) -> None:
             for i in range(warm):
                 leg_step(i)
             lms = _time_steps(leg_step, steps, dist, world)
-            res = {"ms_per_step": lms, "steps": steps, "work_per_step": work(ps[0]), "per_gpu": work(ps[0]) / (lms * 1e-3) / unit_scale}
+            res = {"ms_per_step": lms, "ms_fastest_rank": _time_steps.last_min, "steps": steps, "work_per_step": work(ps[0]),
+                   "per_gpu": work(ps[0]) / (lms * 1e-3) / unit_scale}
             res.update(extra(ps[0], res))
             del ps, os_
             torch.cuda.empty_cache()
@@ -392,7 +529,7 @@ def run_ours(args) -> None:
     # ---- decode workload: bf16 KV cache and e4m3 KV cache ----
     def decode_leg(kv_dtype):
         try:
-            dp = W.paged_decode_on_device(dev, seed=rank, kv_dtype=kv_dtype)   # the 8.5 GB pool is drawn on the GPU
+            dp = W.paged_decode_on_device(dev, seed=rank, kv_dtype=kv_dtype, B=args.decode_batch)   # the pool is drawn on the GPU
             kvb = dp.kv_bytes()
             dout = torch.empty(dp.q.shape[0], dp.q.shape[1], dp.v.shape[-1], device=dev, dtype=torch.bfloat16)
             nspl = capi.num_splits(dp.q, dp.k, dp.v, **dp.capi_kw())
@@ -405,7 +542,7 @@ def run_ours(args) -> None:
             dms = _time_steps(dstep, nsteps, dist, world)
             gbs = kvb / (dms * 1e-3) / 1e9
             res = {
-                "metric": f"paged decode HBM GB/s (B=128 q_len=1 ctx 1k..32k page 64 Hq=32 Hkv=8 d=128 {kv_dtype} KV, "
+                "metric": f"paged decode HBM GB/s (B={args.decode_batch} q_len=1 ctx 1k..32k page 64 Hq=32 Hkv=8 d=128 {kv_dtype} KV, "
                           "leftpad 0..63)",
                 "value": gbs * world, "unit": "GB/s", "ms_per_step": dms, "kv_bytes_per_step": kvb,
                 "num_splits": nspl,
@@ -462,6 +599,7 @@ def run_ours(args) -> None:
         "c1": legs.get("c1"), "c2_fp8": legs.get("c2_fp8"), "c3": legs.get("c3"), "c5": longctx, "longctx": longctx,
         "cpu_baseline": cpu,
         "kernels_per_step": {"prefill": ["fwd_prefill_tc_kernel"], "decode": ["sched_kernel", "fwd_decode_kernel"]},
+        "build": _build_record(),
     }
     print(json.dumps(line))
     if world > 1:
@@ -547,10 +685,17 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-kernel"])
+    ap.add_argument("--ab-shapes", default=",".join(AB_SHAPES), help="--impl reference-kernel: shapes to compare")
+    ap.add_argument("--ab-one", default=None, help=argparse.SUPPRESS)
+    ap.add_argument("--ab-timeout", type=float, default=240.0, help="--impl reference-kernel: seconds per shape")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode workloads")
     ap.add_argument("--no-longctx", action="store_true", help="skip the long-context (KV-sharded) leg")
     ap.add_argument("--headline-only", action="store_true", help="only the headline prefill leg (profiler captures)")
+    ap.add_argument("--decode-only", action="store_true", help="only the two decode legs (profiler captures)")
+    ap.add_argument("--decode-ctx-max", type=int, default=32768, help="--decode-only: longest context (captures use a smaller pool)")
+    ap.add_argument("--decode-batch", type=int, default=128, help="decode batch (128 = the benchmark configuration; "
+                    "smaller values are for profiler captures only)")
     ap.add_argument("--longctx-merge", default="all_gather", choices=["all_gather", "all_to_all"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
@@ -562,8 +707,12 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-kernel":
+        run_ab_one(args.ab_one) if args.ab_one else run_ab(args)
     elif args.workload == "longctx":
         run_longctx(args)
+    elif args.decode_only:
+        run_decode_only(args)
     else:
         run_ours(args)
 

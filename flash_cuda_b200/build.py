@@ -16,7 +16,7 @@ from concurrent.futures import ThreadPoolExecutor
 
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
-LIB = os.path.join(PKG, "lib")
+LIB = os.environ.get("FA_B200_LIB_DIR") or os.path.join(PKG, "lib")   # FA_B200_LIB_DIR: use (or build into) another directory
 OBJ = os.path.join(LIB, "obj")
 INCLUDE = os.path.join(os.path.dirname(PKG), "include")
 CAPI_SO = os.path.join(LIB, "libfa_b200.so")
@@ -86,7 +86,42 @@ def build_capi(force=False, verbose=False) -> str:
             list(ex.map(one, jobs))
     if jobs or not os.path.isfile(CAPI_SO):
         _run([NVCC, "-shared", "-o", CAPI_SO] + objs + ["-lcudart"], verbose)
+        _write_build_info(len(jobs))
     return CAPI_SO
+
+
+BUILD_INFO = os.path.join(LIB, "build_info.json")
+
+
+def sources_digest() -> str:
+    """Digest of every source the C-ABI library is compiled from (kernels, headers, flags)."""
+    paths = [os.path.join(CSRC, f) for f in CU_SOURCES + HEADERS] + [os.path.join(INCLUDE, "fa_b200.h")]
+    return _digest(paths, " ".join(NVCC_FLAGS))
+
+
+def _write_build_info(compiled: int) -> None:
+    import json
+    import time
+    try:
+        ver = subprocess.run([NVCC, "--version"], stdout=subprocess.PIPE, text=True).stdout.strip().splitlines()[-1]
+    except Exception:
+        ver = "unknown"
+    with open(BUILD_INFO, "w") as f:
+        json.dump({"sources_sha256": sources_digest(), "nvcc": ver, "built_at": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime()),
+                   "objects_compiled": compiled, "flags": NVCC_FLAGS}, f)
+
+
+def build_record() -> dict:
+    """What the loaded library was built from, and whether that still matches the sources in the tree: lets a
+    benchmark line say which binary produced it."""
+    import json
+    rec = {"lib": os.path.relpath(CAPI_SO, os.path.dirname(PKG)), "present": os.path.isfile(CAPI_SO)}
+    if os.path.isfile(BUILD_INFO):
+        with open(BUILD_INFO) as f:
+            info = json.load(f)
+        rec.update(sources_sha16=info.get("sources_sha256", "")[:16], built_at=info.get("built_at"), nvcc=info.get("nvcc"),
+                   matches_tree=info.get("sources_sha256") == sources_digest())
+    return rec
 
 
 def build_torch_op(force=False, verbose=False, namespace="_vllm_fa3_C") -> str:

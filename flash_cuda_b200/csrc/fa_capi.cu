@@ -13,7 +13,8 @@
 
 namespace fa {
 
-int launch_sched(const FaSchedParams& sp, const Plan& pl, int32_t* out_dev, int32_t* zero_words, cudaStream_t stream);
+int launch_sched(const FaSchedParams& sp, const Plan& pl, int32_t* out_dev, int32_t* zero_words, cudaStream_t stream,
+                 int row_class = 0, int class_rows = 0);
 int launch_selftest_timeout(DeviceStatus* status, long long max_cycles, cudaStream_t stream);
 int launch_append_kv(const FaAppendParams& p, int num_sms, cudaStream_t stream);
 int launch_combine_strided(const float* o_part, const float* lse_part, int64_t o_split_stride, int64_t lse_split_stride,
@@ -22,6 +23,7 @@ int launch_combine_strided(const float* o_part, const float* lse_part, int64_t o
 int launch_decode(const KParams& kp, const Plan& pl, int compute_dtype, cudaStream_t stream);
 int launch_prefill_tc(const KParams& kp, const Plan& pl, int compute_dtype, cudaStream_t stream);
 bool prefill_tc_supported(const PlanInput& in);
+bool prefill_tc_single_tile(int hd, int hdv);
 bool decode_supported(const PlanInput& in);
 bool prefill_tc_layout_ok(const FaFwdParams* p);
 
@@ -101,7 +103,7 @@ Plan make_plan(const PlanInput& in) {
   }
   pl.route = route;
   if (route == FA_ROUTE_PREFILL_TC) {
-    pl.tile_m = 256; pl.tile_n = 128; pl.rows_per_token = 1;
+    pl.tile_m = prefill_tc_single_tile(in.hd, in.hdv) ? 128 : 256; pl.tile_n = 128; pl.rows_per_token = 1;
   } else if (route == FA_ROUTE_DECODE) {
     pl.tile_m = 16; pl.tile_n = 64; pl.rows_per_token = rep;
   } else {
@@ -160,10 +162,29 @@ static PlanInput plan_input(const FaSchedParams* p, int num_sms) {
   return in;
 }
 
+// A batch that mixes decode-shaped sequences (a few query rows) with prefill-shaped ones: when both kernels take the
+// shape and the sequences are ragged enough (the mean query length is under a quarter of the maximum), one call runs
+// BOTH kernels, each over its own work list (the reference splits such a batch into two launches as well,
+// kernels/fa4_blackwell.cu:9995-10021).  Decided from host-side facts only; a list for either kernel may turn out empty.
+static bool mixed_batch(const FaFwdParams* p, const PlanInput& in, const Plan& pl) {
+  if (p->route != FA_ROUTE_AUTO || pl.route != FA_ROUTE_PREFILL_TC || p->scheduler_metadata != nullptr) return false;
+  if (p->batch < 2 || !decode_supported(in) || p->out_dtype == FA_DT_FP32) return false;
+  return (long long)p->total_q * 4 < (long long)p->batch * p->max_seqlen_q;
+}
+static Plan decode_part_plan(const PlanInput& in, const Plan& pl) {
+  Plan d = pl;
+  d.route = FA_ROUTE_DECODE;
+  d.tile_m = 16; d.tile_n = 64; d.rows_per_token = in.hq / in.hkv;
+  d.max_mtiles = kDecodeMaxRows / 16;
+  d.nsplits = 1;
+  return d;
+}
+
 // ---- workspace layout ----
 struct WsLayout {
   size_t header;      // DeviceStatus @0, counters @64
   size_t work_off, work_bytes;
+  size_t work2_off, work2_bytes;   // mixed batches: the prefill kernel's list
   size_t lse_off, lse_bytes;
   size_t o_off, o_bytes;
   size_t total;
@@ -176,6 +197,18 @@ static WsLayout ws_layout(const FaFwdParams* p, const Plan& pl) {
   w.work_bytes = (pl.route == FA_ROUTE_DECODE && p->scheduler_metadata == nullptr)
                      ? align_up((size_t)sched_len(pl, p->batch) * 4, 256) : 0;
   off += w.work_bytes;
+  if (pl.route == FA_ROUTE_PREFILL_TC && p->scheduler_metadata == nullptr && p->batch >= 2) {
+    // room for the two lists of a mixed batch (whether the call is one is decided from the same facts in fa_b200_fwd)
+    const PlanInput in = plan_input(p, pl.num_sms);
+    if (mixed_batch(p, in, pl)) {
+      w.work_off = off;
+      w.work_bytes = align_up((size_t)sched_len(decode_part_plan(in, pl), p->batch) * 4, 256);
+      off += w.work_bytes;
+      w.work2_off = off;
+      w.work2_bytes = align_up((size_t)sched_len(pl, p->batch) * 4, 256);
+      off += w.work2_bytes;
+    }
+  }
   if (pl.nsplits > 1) {
     w.lse_off = off;
     w.lse_bytes = align_up((size_t)pl.nsplits * p->hq * p->total_q * 4, 256);
@@ -326,6 +359,27 @@ int fa_b200_fwd(const FaFwdParams* p, void* workspace, size_t workspace_bytes, f
     }
     kp.work = work;
     rc = note_cuda_error(launch_decode(kp, pl, compute_dtype, stream), "decode kernel");
+  } else if (pl.route == FA_ROUTE_PREFILL_TC && w.work2_bytes > 0) {
+    // mixed batch: two work lists, the decode kernel over the short sequences, then the prefill kernel over the rest
+    FaSchedParams sp{};
+    sp.seqused_k = p->seqused_k; sp.cu_seqlens_q = p->cu_seqlens_q; sp.cu_seqlens_k = p->cu_seqlens_k;
+    sp.leftpad_k = p->leftpad_k; sp.batch = p->batch; sp.max_seqlen_q = p->max_seqlen_q;
+    sp.max_seqlen_k = p->max_seqlen_k; sp.hq = p->hq; sp.hkv = p->hkv; sp.hd = p->hd; sp.hdv = p->hdv;
+    sp.is_causal = in.is_causal; sp.window_left = in.window_left; sp.window_right = in.window_right;
+    const Plan pd = decode_part_plan(in, pl);
+    int32_t* list_d = (int32_t*)(ws + w.work_off);
+    int32_t* list_p = (int32_t*)(ws + w.work2_off);
+    rc = note_cuda_error(launch_sched(sp, pd, list_d, nullptr, stream, 1, kDecodeMaxRows), "sched_kernel");
+    if (rc == FA_OK) rc = note_cuda_error(launch_sched(sp, pl, list_p, nullptr, stream, 2, kDecodeMaxRows), "sched_kernel");
+    if (rc != FA_OK) return rc;
+    KParams kd = kp;
+    kd.work = list_d;
+    kd.nsplits = 1;
+    kd.work_expect = SchedExpect{p->batch, 1, pd.tile_m, pd.tile_n, pd.max_mtiles, pd.rows_per_token, pd.route};
+    rc = note_cuda_error(launch_decode(kd, pd, compute_dtype, stream), "decode kernel");
+    if (rc != FA_OK) return rc;
+    kp.work = list_p;
+    rc = note_cuda_error(launch_prefill_tc(kp, pl, compute_dtype, stream), "tcgen05 prefill kernel");
   } else if (pl.route == FA_ROUTE_PREFILL_TC) {
     kp.work = p->scheduler_metadata;   // optional: the sorted (batch, tile) list replaces the arithmetic order
     rc = note_cuda_error(launch_prefill_tc(kp, pl, compute_dtype, stream), "tcgen05 prefill kernel");

@@ -105,6 +105,9 @@ struct SchedArgs {
   int32_t sorted;          // E <= kSchedSortMax and every block count fits the key (host decision, fa_sched.h)
   int32_t sort_n;          // power of two >= E
   int32_t* zero_words;     // when not null: 64 words (a workspace header) this kernel clears for the kernel after it
+  int32_t row_class;       // 0: every sequence; 1: only sequences with at most class_rows packed query rows per kv head
+  int32_t class_rows;      //    (the decode kernel's share of a mixed batch); 2: only the others (the prefill kernel's)
+  int32_t class_rep;       // q heads per kv head, for the row count of the class test
 };
 
 __device__ __forceinline__ bool sched_entry(const SchedArgs& a, int e, int* b_out, int* mt_out, int* lo, int* hi) {
@@ -117,6 +120,10 @@ __device__ __forceinline__ bool sched_entry(const SchedArgs& a, int e, int* b_ou
   *b_out = b;
   *mt_out = mt;
   if (row0 >= rows_total) { *lo = 0; *hi = 0; return false; }
+  if (a.row_class != 0) {
+    const bool small = seqlen_q * a.class_rep <= a.class_rows;
+    if (small != (a.row_class == 1)) { *lo = 0; *hi = 0; return false; }
+  }
   const int tok_min = row0 / a.rows_per_token;
   const int tok_max = min(seqlen_q - 1, (row0 + a.tile_m - 1) / a.rows_per_token);
   nblock_range(seqlen_k, leftpad, seqlen_k - seqlen_q + tok_min, seqlen_k - seqlen_q + tok_max, a.is_causal,
@@ -224,7 +231,8 @@ int launch_selftest_timeout(DeviceStatus* status, long long max_cycles, cudaStre
   return (int)cudaGetLastError();
 }
 
-int launch_sched(const FaSchedParams& sp, const Plan& pl, int32_t* out_dev, int32_t* zero_words, cudaStream_t stream) {
+int launch_sched(const FaSchedParams& sp, const Plan& pl, int32_t* out_dev, int32_t* zero_words, cudaStream_t stream,
+                 int row_class, int class_rows) {
   SchedArgs a;
   a.seqused_k = sp.seqused_k; a.cu_q = sp.cu_seqlens_q; a.cu_k = sp.cu_seqlens_k; a.leftpad_k = sp.leftpad_k;
   a.batch = sp.batch; a.max_seqlen_q = sp.max_seqlen_q; a.max_seqlen_k = sp.max_seqlen_k;
@@ -236,6 +244,7 @@ int launch_sched(const FaSchedParams& sp, const Plan& pl, int32_t* out_dev, int3
   a.sort_n = 1;
   while (a.sort_n < E) a.sort_n <<= 1;
   a.zero_words = zero_words;
+  a.row_class = row_class; a.class_rows = class_rows; a.class_rep = sp.hkv > 0 ? sp.hq / sp.hkv : 1;
   const size_t smem = a.sorted ? (size_t)a.sort_n * sizeof(uint32_t) : 0;
   const int threads = (a.sorted && a.sort_n < 1024) ? (a.sort_n < 64 ? 64 : a.sort_n) : 1024;
   sched_kernel<<<1, threads, smem, stream>>>(a, out_dev);

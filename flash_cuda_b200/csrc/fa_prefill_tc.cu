@@ -55,7 +55,8 @@ constexpr int kTwoTermBlocks = 2;   // e4m3: tiles that see at most this many ke
 struct TcArgs {
   KParams kp;
   int num_items;     // batch * hq * max_pairs: the work ids of the arithmetic order (an upper bound with a list)
-  int max_pairs;
+  int max_pairs;     // work items per (batch, head): ceil(max_seqlen_q / rows per item)
+  int item_rows;     // query rows per work item: 256 (two tiles) or 128 (one tile: head dims whose O needs > 128 columns)
   int use_list;      // kp.work holds scheduler metadata of this route: items = its valid entries x hq
   int stage_out;     // map_o is valid: full 32-row groups leave through shared memory and TMA stores
   int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128)
@@ -78,9 +79,9 @@ template <> struct Elem<fp8_t> {
 
 constexpr int kSmemLimit = 232448;   // dynamic shared memory one CTA may ask for on sm_100
 
-template <int ESZ, int HD, int HDV, int KST, int VST>
+template <int ESZ, int HD, int HDV, int KST, int VST, int NTL>
 struct Smem {
-  static constexpr int kQBytes = 2 * TM * HD * ESZ;
+  static constexpr int kQBytes = NTL * TM * HD * ESZ;
   static constexpr int kKStage = TN * HD * ESZ;
   static constexpr int kVStage = TN * HDV * ESZ;
   static constexpr int kRings = kQBytes + KST * kKStage + VST * kVStage;
@@ -105,12 +106,14 @@ struct alignas(16) Item {
 };
 static_assert(sizeof(Item) == 64, "mailbox slot");
 
+template <int NTL>
 __device__ __forceinline__ Item decode_item(const TcArgs& a, int w, bool* bad_entry) {
+  constexpr int kItemRows = NTL * TM;
   const KParams& p = a.kp;
   Item it;
   it.w = w;
   if (a.use_list) {
-    // entry e of the sorted list = (batch, 256-row tile); all q heads of one entry are consecutive work ids
+    // entry e of the sorted list = (batch, tile of item_rows rows); all q heads of one entry are consecutive work ids
     const int e = w / p.hq;
     it.h = w - e * p.hq;
     const int32_t* ent = p.work + kSchedHeader + 4 * e;
@@ -134,14 +137,14 @@ __device__ __forceinline__ Item decode_item(const TcArgs& a, int w, bool* bad_en
   it.k0 = p.page_table ? 0 : p.cu_k[it.b];
   it.seqlen_k = p.seqused_k ? p.seqused_k[it.b] : (p.cu_k[it.b + 1] - p.cu_k[it.b]);
   it.leftpad = p.leftpad_k ? p.leftpad_k[it.b] : 0;
-  it.valid = it.pair * 2 * TM < it.seqlen_q;
+  it.valid = it.pair * kItemRows < it.seqlen_q;
   it.ulo = 0x7fffffff;
   it.uhi = 0;
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    const int row0 = it.pair * 2 * TM + t * TM;
+    const int row0 = it.pair * kItemRows + t * TM;
     it.lo[t] = it.hi[t] = 0;
-    if (it.valid && row0 < it.seqlen_q) {
+    if (it.valid && row0 < it.seqlen_q && t < NTL) {
       const int rmax = min(it.seqlen_q - 1, row0 + TM - 1);
       nblock_range(it.seqlen_k, it.leftpad, it.seqlen_k - it.seqlen_q + row0, it.seqlen_k - it.seqlen_q + rmax,
                    p.is_causal, p.window_left, p.window_right, TN, &it.lo[t], &it.hi[t]);
@@ -162,7 +165,10 @@ struct Ring {
   }
 };
 
-template <typename T, int HD, int HDV, int KST, int VST>
+// NTL = query tiles per work item: 2, or 1 where one tile's S (128 columns) and O (HDV > 128 columns) leave no room
+// in the 512 TMEM columns for a second tile (head_dim 256, head_dim 192 with 192 value columns).  With one tile the
+// second softmax warpgroup stays idle and softmax and MMAs of the tile alternate instead of overlapping.
+template <typename T, int HD, int HDV, int KST, int VST, int NTL>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -171,7 +177,10 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
   constexpr bool F8 = Elem<T>::kF8;
   constexpr int EPB = 128 / ESZ;               // elements per 128-byte swizzle row
   using TO = typename Elem<T>::Out;
-  using SM = Smem<ESZ, HD, HDV, KST, VST>;
+  using SM = Smem<ESZ, HD, HDV, KST, VST, NTL>;
+  static_assert(NTL == 2 ? HDV <= 128 : HDV <= 256, "TMEM: NTL x (128 S columns + HDV O columns) <= 512");
+  constexpr uint32_t O_BASE = NTL * TN;        // first TMEM column of the O accumulators
+  constexpr uint32_t O_STRIDE = NTL == 2 ? 128 : 0;
   const KParams& p = a.kp;
   extern __shared__ unsigned char smem_dyn[];
   // 1024-byte alignment for the 128-byte swizzle atoms, by rounding up inside a request that carries 1 KB of slack.
@@ -217,7 +226,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     mbar_init(bar_drain, 1);
     mbar_init(bar_k0_full, 1);
     for (int s = 0; s < KST; ++s) mbar_init(bar_k_full + 8 * s, 1);
-    for (int i = 0; i < 2; ++i) { mbar_init(bar_w_full + 8 * i, 1); mbar_init(bar_w_empty + 8 * i, 9); }
+    for (int i = 0; i < 2; ++i) { mbar_init(bar_w_full + 8 * i, 1); mbar_init(bar_w_empty + 8 * i, 1 + 4 * NTL); }
     s_abort[0] = 0;
     s_abort[1] = 0;   // [1] is never raised: waits that may only end by completion or time limit
     mbar_fence_init();
@@ -270,7 +279,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           first_ticket = false;
           if (w >= num_items) { it.w = kEndOfWork; break; }
           bool bad = false;
-          it = decode_item(a, w, &bad);   // sequence bounds are read from global memory once per item
+          it = decode_item<NTL>(a, w, &bad);   // sequence bounds are read from global memory once per item
           if (bad) { report_error(p.status, DEV_ERR_BAD_INDEX, ROLE_TMA); num_items = 0; it.w = kEndOfWork; break; }
           if (it.valid) break;
         }
@@ -293,11 +302,11 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         // then spread over two blocks instead of one.  Order: Q tile 0, K of the first block, Q tile 1.
         auto load_q = [&](int t) -> bool {
           if (!wait_or_abort(bar_q_empty + 8 * t, (qcnt & 1) ^ 1, s_abort)) return false;
-          mbar_expect_tx(bar_q_full + 8 * t, SM::kQBytes / 2);
+          mbar_expect_tx(bar_q_full + 8 * t, TM * HD * ESZ);
 #pragma unroll
           for (int cb = 0; cb < HD / EPB; ++cb)
             tma_load_3d(sQ + t * (TM * HD * ESZ) + cb * (TM * 128), &map_q, cb * EPB, it.h,
-                        it.q0 + it.pair * 2 * TM + t * TM, bar_q_full + 8 * t);
+                        it.q0 + it.pair * (NTL * TM) + t * TM, bar_q_full + 8 * t);
           return true;
         };
         ok = load_q(0);
@@ -333,8 +342,10 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
           kr.advance();
           ++k0cnt;
         }
-        ok = load_q(1);
-        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+        if constexpr (NTL == 2) {
+          ok = load_q(1);
+          if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+        }
         ++qcnt;
         for (int nb = it.ulo; nb < it.uhi; ++nb) {
           const bool nxt = nb + 1 < it.uhi;
@@ -358,7 +369,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       // drain: every copy this thread issued must have landed before the CTA may leave
       if (qcnt > 0) {
         wait_or_abort(bar_q_full, (qcnt - 1) & 1, s_abort + 1 /* never set: pure time limit */);
-        wait_or_abort(bar_q_full + 8, (qcnt - 1) & 1, s_abort + 1);
+        if constexpr (NTL == 2) wait_or_abort(bar_q_full + 8, (qcnt - 1) & 1, s_abort + 1);
       }
       if constexpr (MERGE_KV) {
         if (k0cnt > 0) wait_or_abort(bar_k0_full, (k0cnt - 1) & 1, s_abort + 1);
@@ -426,13 +437,13 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       if (leader) {
 #pragma unroll
         for (int ks = 0; ks < TN / KEL; ++ks)   // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
-          umma_ts<F8>(tmem_u + 256 + t * 128, tmem_u + t * TN + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
+          umma_ts<F8>(tmem_u + O_BASE + t * O_STRIDE, tmem_u + t * TN + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
                       (!first || ks > 0) ? 1u : 0u);
         if constexpr (F8) {
           if (two_term) {
 #pragma unroll
             for (int ks = 0; ks < TN / KEL; ++ks)
-              umma_ts<F8>(tmem_u + 256 + t * 128, tmem_u + t * TN + 32 + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)),
+              umma_ts<F8>(tmem_u + O_BASE + t * O_STRIDE, tmem_u + t * TN + 32 + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)),
                           idesc_pv, 1u);
           }
         }
@@ -469,7 +480,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         else wait(bar_k_full + 8 * ks, kr.phase);
         ++k0cnt;
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
+        for (int t = 0; t < NTL; ++t) {
           wait(bar_q_full + 8 * t, qcnt & 1);
           if (ulo >= lo[t] && ulo < hi[t]) issue_qk(t, ks);
           // tile t's only QK of this item (or it has none): its Q slot may be refilled once that has run
@@ -486,7 +497,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
         wait(bar_v_full + 8 * vs, vr.phase);   // V of this block (and, with merged barriers, K of the next one)
         bool k_ready = MERGE_KV;
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
+        for (int t = 0; t < NTL; ++t) {
           if (i >= lo[t] && i < hi[t]) {
             const bool first = i == lo[t];
             if (first) {   // O_t is overwritten: the previous item's epilogue must have read it
@@ -526,7 +537,7 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
     const int r = (warp & 3) * 32 + lane;          // row within the tile == TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_base + t * TN;
-    const uint32_t tO = tmem + lane_base + 256 + t * 128;
+    const uint32_t tO = tmem + lane_base + O_BASE + t * O_STRIDE;
     const bool has_cap = p.softcap > 0.f;
     uint32_t scnt = 0, ocnt = 0;
     bool ok = true;
@@ -546,9 +557,12 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       ++wcnt;
       return it;
     };
-    for (Item it = next_work(); it.w != kEndOfWork && ok; it = next_work()) {
+    // (with one tile per item the second softmax warpgroup has no rows: it takes no part in the hand-offs)
+    const bool has_tile = NTL == 2 || t == 0;
+    for (Item it = (has_tile ? next_work() : Item{0, 0, 0, 0, 0, 0, 0, 0, {0, 0}, {0, 0}, 0, 0, 0, kEndOfWork});
+         it.w != kEndOfWork && ok; it = next_work()) {
       if (!it.valid) continue;
-      const int row0 = it.pair * 2 * TM + t * TM;
+      const int row0 = it.pair * (NTL * TM) + t * TM;
       if (row0 >= it.seqlen_q) continue;           // this tile owns no row
       const int row = row0 + r;
       const int hk = it.h / p.rep;
@@ -713,106 +727,206 @@ fwd_prefill_tc_kernel(const TcArgs a, const __grid_constant__ CUtensorMap map_q,
       if (!ok) break;
 
       // ---- epilogue of this tile ----
-      // The whole O row goes to registers first and O_t is released at once: the MMA warp may start the next
-      // item's first PV while this thread is still normalising and storing.
-      const bool had_blocks = it.hi[t] > it.lo[t];
-      uint32_t o[HDV / 32][32];
-      if (had_blocks) {
-        ok = wait_or_abort(bar_o_full + 8 * t, ocnt & 1, s_abort);
-        ++ocnt;
-        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_EPILOGUE); break; }
-        tc_fence_after_sync();
-#pragma unroll
-        for (int c = 0; c < HDV / 32; ++c) tmem_ld32(tO + c * 32, o[c]);
-        tmem_wait_ld();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_o_empty + 8 * t);
-      } else {
-#pragma unroll
-        for (int c = 0; c < HDV / 32; ++c)
-#pragma unroll
-          for (int j = 0; j < 32; ++j) o[c][j] = 0u;
-      }
-      float m_fin = m_used, l_fin = l, osc = 1.f;
-      float l_norm = F8 ? lr : l;          // what O is divided by
-      if (p.s_aux) {
-        const float ys = p.s_aux[it.h] * kLog2e;
-        const float mn = fmaxf(m_used, ys);
-        osc = (m_used == -INFINITY) ? 0.f : ex2(m_used - mn);
-        const float sink = ex2(ys - mn);
-        l_fin = l * osc + sink;
-        l_norm = l_norm * osc + sink;
-        m_fin = mn;
-      }
-      const float inv = l_norm > 0.f ? osc * vds / l_norm : 0.f;
-      const float2 inv2 = make_float2(inv, inv);
-      const bool row_ok = row < it.seqlen_q;
-      const int wrow0 = row0 + (warp & 3) * 32;            // first row of this warp's 32
-      bool staged = false;
-      if constexpr (SM::kStageOut) staged = a.stage_out && (wrow0 + 32 <= it.seqlen_q);   // warp-uniform
-      if (staged) {
-        if constexpr (SM::kStageOut) {
-          const uint32_t stg = base + SM::kStageOff + (uint32_t)warp * 4096u;
-#pragma unroll
-          for (int hf = 0; hf < HDV / 64; ++hf) {
-            uint32_t pk[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float2 v = fmul2(make_float2(__uint_as_float(o[2 * hf + (j >> 4)][(2 * j) & 31]),
-                                                 __uint_as_float(o[2 * hf + (j >> 4)][((2 * j) & 31) + 1])), inv2);
-              pk[j] = pack2<TO>(v.x, v.y);
-            }
-            // the store issued for the previous 64 columns (or the previous item) must have read the buffer
-            if (lane == 0) bulk_wait_read_all();
-            __syncwarp();
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {   // 16-byte chunk c of row `lane`, at its 128-byte-swizzle position
-              const uint32_t addr = stg + (uint32_t)lane * 128u + ((uint32_t)(c ^ (lane & 7)) << 4);
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
-                           "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              tma_store_3d(&map_o, stg, hf * 64, it.h, it.q0 + wrow0);
-              bulk_commit_group();
-            }
-          }
-        }
-      } else if (row_ok) {
-        if (p.out_f32) {
-          float* op = reinterpret_cast<float*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
-#pragma unroll
-          for (int c = 0; c < HDV / 32; ++c) {
-            if (c * 32 < a.out_cols) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(op + c * 32 + j) =
-                    make_float4(__uint_as_float(o[c][j]) * inv, __uint_as_float(o[c][j + 1]) * inv,
-                                __uint_as_float(o[c][j + 2]) * inv, __uint_as_float(o[c][j + 3]) * inv);
-            }
-          }
+      if constexpr (HDV <= 128) {
+        // The whole O row goes to registers first and O_t is released at once: the MMA warp may start the next
+        // item's first PV while this thread is still normalising and storing.
+        const bool had_blocks = it.hi[t] > it.lo[t];
+        uint32_t o[HDV / 32][32];
+        if (had_blocks) {
+          ok = wait_or_abort(bar_o_full + 8 * t, ocnt & 1, s_abort);
+          ++ocnt;
+          if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_EPILOGUE); break; }
+          tc_fence_after_sync();
+  #pragma unroll
+          for (int c = 0; c < HDV / 32; ++c) tmem_ld32(tO + c * 32, o[c]);
+          tmem_wait_ld();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_o_empty + 8 * t);
         } else {
-          TO* op = reinterpret_cast<TO*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
-#pragma unroll
-          for (int c = 0; c < HDV / 32; ++c) {
-            if (c * 32 < a.out_cols) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 v;
-                v.x = pack2<TO>(__uint_as_float(o[c][j]) * inv, __uint_as_float(o[c][j + 1]) * inv);
-                v.y = pack2<TO>(__uint_as_float(o[c][j + 2]) * inv, __uint_as_float(o[c][j + 3]) * inv);
-                v.z = pack2<TO>(__uint_as_float(o[c][j + 4]) * inv, __uint_as_float(o[c][j + 5]) * inv);
-                v.w = pack2<TO>(__uint_as_float(o[c][j + 6]) * inv, __uint_as_float(o[c][j + 7]) * inv);
-                *reinterpret_cast<uint4*>(op + c * 32 + j) = v;
+  #pragma unroll
+          for (int c = 0; c < HDV / 32; ++c)
+  #pragma unroll
+            for (int j = 0; j < 32; ++j) o[c][j] = 0u;
+        }
+        float m_fin = m_used, l_fin = l, osc = 1.f;
+        float l_norm = F8 ? lr : l;          // what O is divided by
+        if (p.s_aux) {
+          const float ys = p.s_aux[it.h] * kLog2e;
+          const float mn = fmaxf(m_used, ys);
+          osc = (m_used == -INFINITY) ? 0.f : ex2(m_used - mn);
+          const float sink = ex2(ys - mn);
+          l_fin = l * osc + sink;
+          l_norm = l_norm * osc + sink;
+          m_fin = mn;
+        }
+        const float inv = l_norm > 0.f ? osc * vds / l_norm : 0.f;
+        const float2 inv2 = make_float2(inv, inv);
+        const bool row_ok = row < it.seqlen_q;
+        const int wrow0 = row0 + (warp & 3) * 32;            // first row of this warp's 32
+        bool staged = false;
+        if constexpr (SM::kStageOut) staged = a.stage_out && (wrow0 + 32 <= it.seqlen_q);   // warp-uniform
+        if (staged) {
+          if constexpr (SM::kStageOut) {
+            const uint32_t stg = base + SM::kStageOff + (uint32_t)warp * 4096u;
+  #pragma unroll
+            for (int hf = 0; hf < HDV / 64; ++hf) {
+              uint32_t pk[32];
+  #pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float2 v = fmul2(make_float2(__uint_as_float(o[2 * hf + (j >> 4)][(2 * j) & 31]),
+                                                   __uint_as_float(o[2 * hf + (j >> 4)][((2 * j) & 31) + 1])), inv2);
+                pk[j] = pack2<TO>(v.x, v.y);
+              }
+              // the store issued for the previous 64 columns (or the previous item) must have read the buffer
+              if (lane == 0) bulk_wait_read_all();
+              __syncwarp();
+  #pragma unroll
+              for (int c = 0; c < 8; ++c) {   // 16-byte chunk c of row `lane`, at its 128-byte-swizzle position
+                const uint32_t addr = stg + (uint32_t)lane * 128u + ((uint32_t)(c ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
+                             "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&map_o, stg, hf * 64, it.h, it.q0 + wrow0);
+                bulk_commit_group();
+              }
+            }
+          }
+        } else if (row_ok) {
+          if (p.out_f32) {
+            float* op = reinterpret_cast<float*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
+  #pragma unroll
+            for (int c = 0; c < HDV / 32; ++c) {
+              if (c * 32 < a.out_cols) {
+  #pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<float4*>(op + c * 32 + j) =
+                      make_float4(__uint_as_float(o[c][j]) * inv, __uint_as_float(o[c][j + 1]) * inv,
+                                  __uint_as_float(o[c][j + 2]) * inv, __uint_as_float(o[c][j + 3]) * inv);
+              }
+            }
+          } else {
+            TO* op = reinterpret_cast<TO*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride;
+  #pragma unroll
+            for (int c = 0; c < HDV / 32; ++c) {
+              if (c * 32 < a.out_cols) {
+  #pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 v;
+                  v.x = pack2<TO>(__uint_as_float(o[c][j]) * inv, __uint_as_float(o[c][j + 1]) * inv);
+                  v.y = pack2<TO>(__uint_as_float(o[c][j + 2]) * inv, __uint_as_float(o[c][j + 3]) * inv);
+                  v.z = pack2<TO>(__uint_as_float(o[c][j + 4]) * inv, __uint_as_float(o[c][j + 5]) * inv);
+                  v.w = pack2<TO>(__uint_as_float(o[c][j + 6]) * inv, __uint_as_float(o[c][j + 7]) * inv);
+                  *reinterpret_cast<uint4*>(op + c * 32 + j) = v;
+                }
               }
             }
           }
         }
+        if (row_ok)
+          p.lse[(int64_t)it.h * p.total_q + it.q0 + row] = l_fin > 0.f ? (m_fin + lg2(l_fin)) * kLn2 : -INFINITY;
+      } else {
+        // HDV > 128 (one tile per item): the O row is read 64 columns at a time; O_t is released as soon as its last
+        // column has been read.  Each 64-column group leaves like a half row of the two-tile form: staged + one TMA
+        // store where the warp's 32 rows all lie inside the sequence, direct stores otherwise.
+        constexpr int NG = HDV / 64;
+        const bool had_blocks = it.hi[t] > it.lo[t];
+        if (had_blocks) {
+          ok = wait_or_abort(bar_o_full + 8 * t, ocnt & 1, s_abort);
+          ++ocnt;
+          if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_EPILOGUE); break; }
+          tc_fence_after_sync();
+        }
+        float m_fin = m_used, l_fin = l, osc = 1.f;
+        float l_norm = F8 ? lr : l;          // what O is divided by
+        if (p.s_aux) {
+          const float ys = p.s_aux[it.h] * kLog2e;
+          const float mn = fmaxf(m_used, ys);
+          osc = (m_used == -INFINITY) ? 0.f : ex2(m_used - mn);
+          const float sink = ex2(ys - mn);
+          l_fin = l * osc + sink;
+          l_norm = l_norm * osc + sink;
+          m_fin = mn;
+        }
+        const float inv = l_norm > 0.f ? osc * vds / l_norm : 0.f;
+        const float2 inv2 = make_float2(inv, inv);
+        const bool row_ok = row < it.seqlen_q;
+        const int wrow0 = row0 + (warp & 3) * 32;            // first row of this warp's 32
+        bool staged = false;
+        if constexpr (SM::kStageOut) staged = a.stage_out && (wrow0 + 32 <= it.seqlen_q);   // warp-uniform
+#pragma unroll 1
+        for (int g = 0; g < NG; ++g) {
+          uint32_t o[2][32];
+          if (had_blocks) {
+            tmem_ld32(tO + g * 64, o[0]);
+            tmem_ld32(tO + g * 64 + 32, o[1]);
+            tmem_wait_ld();
+            if (g + 1 == NG) {     // the whole row has been read
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(bar_o_empty + 8 * t);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { o[0][j] = 0u; o[1][j] = 0u; }
+          }
+          if (staged) {
+            if constexpr (SM::kStageOut) {
+              const uint32_t stg = base + SM::kStageOff + (uint32_t)warp * 4096u;
+              uint32_t pk[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float2 v = fmul2(make_float2(__uint_as_float(o[j >> 4][(2 * j) & 31]),
+                                                   __uint_as_float(o[j >> 4][((2 * j) & 31) + 1])), inv2);
+                pk[j] = pack2<TO>(v.x, v.y);
+              }
+              if (lane == 0) bulk_wait_read_all();   // the previous store must have read the buffer
+              __syncwarp();
+#pragma unroll
+              for (int c = 0; c < 8; ++c) {   // 16-byte chunk c of row `lane`, at its 128-byte-swizzle position
+                const uint32_t addr = stg + (uint32_t)lane * 128u + ((uint32_t)(c ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(pk[4 * c]), "r"(pk[4 * c + 1]),
+                             "r"(pk[4 * c + 2]), "r"(pk[4 * c + 3]) : "memory");
+              }
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                tma_store_3d(&map_o, stg, g * 64, it.h, it.q0 + wrow0);
+                bulk_commit_group();
+              }
+            }
+          } else if (row_ok) {
+            if (p.out_f32) {
+              float* op = reinterpret_cast<float*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride + g * 64;
+#pragma unroll
+              for (int c = 0; c < 2; ++c)
+#pragma unroll
+                for (int j = 0; j < 32; j += 4)
+                  *reinterpret_cast<float4*>(op + c * 32 + j) =
+                      make_float4(__uint_as_float(o[c][j]) * inv, __uint_as_float(o[c][j + 1]) * inv,
+                                  __uint_as_float(o[c][j + 2]) * inv, __uint_as_float(o[c][j + 3]) * inv);
+            } else {
+              TO* op = reinterpret_cast<TO*>(p.out) + (int64_t)(it.q0 + row) * p.o_row_stride + (int64_t)it.h * p.o_head_stride + g * 64;
+#pragma unroll
+              for (int c = 0; c < 2; ++c)
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  uint4 v;
+                  v.x = pack2<TO>(__uint_as_float(o[c][j]) * inv, __uint_as_float(o[c][j + 1]) * inv);
+                  v.y = pack2<TO>(__uint_as_float(o[c][j + 2]) * inv, __uint_as_float(o[c][j + 3]) * inv);
+                  v.z = pack2<TO>(__uint_as_float(o[c][j + 4]) * inv, __uint_as_float(o[c][j + 5]) * inv);
+                  v.w = pack2<TO>(__uint_as_float(o[c][j + 6]) * inv, __uint_as_float(o[c][j + 7]) * inv);
+                  *reinterpret_cast<uint4*>(op + c * 32 + j) = v;
+                }
+            }
+          }
+        }
+        if (row_ok)
+          p.lse[(int64_t)it.h * p.total_q + it.q0 + row] = l_fin > 0.f ? (m_fin + lg2(l_fin)) * kLn2 : -INFINITY;
       }
-      if (row_ok)
-        p.lse[(int64_t)it.h * p.total_q + it.q0 + row] = l_fin > 0.f ? (m_fin + lg2(l_fin)) * kLn2 : -INFINITY;
     }
     if constexpr (SM::kStageOut) {
       if (lane == 0) bulk_wait_all();   // this lane's output stores have completed before the CTA leaves
@@ -895,12 +1009,13 @@ static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t row
   return true;
 }
 
-template <typename T, int HD, int HDV, int KST, int VST>
+template <typename T, int HD, int HDV, int KST, int VST, int NTL = 2>
 static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_rows, cudaStream_t stream) {
-  using SM = Smem<Elem<T>::kSize, HD, HDV, KST, VST>;
+  using SM = Smem<Elem<T>::kSize, HD, HDV, KST, VST, NTL>;
   TcArgs a;
   a.kp = kp;
-  a.max_pairs = (kp.max_seqlen_q + 2 * TM - 1) / (2 * TM);
+  a.item_rows = NTL * TM;
+  a.max_pairs = (kp.max_seqlen_q + a.item_rows - 1) / a.item_rows;
   a.num_items = kp.batch * kp.hq * a.max_pairs;
   a.use_list = kp.work != nullptr;
   const bool paged = kp.page_table != nullptr;
@@ -921,7 +1036,7 @@ static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
                     (uint64_t)kp.o_row_stride, 32))
       a.stage_out = 1;
   }
-  auto kern = fwd_prefill_tc_kernel<T, HD, HDV, KST, VST>;
+  auto kern = fwd_prefill_tc_kernel<T, HD, HDV, KST, VST, NTL>;
   int smem = SM::kBytes + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;   // one CTA per SM: the CTA owns all 512 TMEM columns
   static std::atomic<unsigned long long> attr_done{0};   // one bit per device
@@ -942,10 +1057,14 @@ static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
 
 // Shapes the tensor-core prefill route takes. Layout conditions (heads back to back inside a row, pages
 // back to back) are checked at launch: fa_b200_fwd re-plans onto the general route when they do not hold.
+// Head dims whose O accumulator leaves TMEM room for one query tile only (work items of 128 rows).
+bool prefill_tc_single_tile(int hd, int hdv) { return (hd == 256 && hdv == 256) || (hd == 192 && hdv == 192); }
+
 bool prefill_tc_supported(const PlanInput& in) {
   if (in.q_dtype != in.kv_dtype) return false;
   const bool hd_ok = (in.hd == 64 && in.hdv == 64) || (in.hd == 128 && in.hdv == 128) || (in.hd == 192 && in.hdv == 128) ||
-                     (in.hd == 96 && in.hdv == 96);   // 96 runs as 128: TMA zero-fills columns 96..127
+                     (in.hd == 96 && in.hdv == 96) ||   // 96 runs as 128: TMA zero-fills columns 96..127
+                     prefill_tc_single_tile(in.hd, in.hdv);
   if (!hd_ok) return false;
   if (in.q_dtype == FA_DT_FP8_E4M3 && !(in.hd == 128 && in.hdv == 128)) return false;   // e4m3: head_dim 128 only
   if (in.page_size > 0) {
@@ -980,6 +1099,12 @@ int launch_prefill_tc(const KParams& kp, const Plan& pl, int dtype, cudaStream_t
   if (kp.hd == 192 && kp.hdv == 128)
     return bf ? tc::launch_impl<__nv_bfloat16, 192, 128, 2, 1>(kp, pl, dtype, kv_rows, stream)
               : tc::launch_impl<__half, 192, 128, 2, 1>(kp, pl, dtype, kv_rows, stream);
+  if (kp.hd == 256 && kp.hdv == 256)
+    return bf ? tc::launch_impl<__nv_bfloat16, 256, 256, 1, 1, 1>(kp, pl, dtype, kv_rows, stream)
+              : tc::launch_impl<__half, 256, 256, 1, 1, 1>(kp, pl, dtype, kv_rows, stream);
+  if (kp.hd == 192 && kp.hdv == 192)
+    return bf ? tc::launch_impl<__nv_bfloat16, 192, 192, 2, 1, 1>(kp, pl, dtype, kv_rows, stream)
+              : tc::launch_impl<__half, 192, 192, 2, 1, 1>(kp, pl, dtype, kv_rows, stream);
   return -1;
 }
 

@@ -6,8 +6,11 @@ own build (bench/eval.py:122-128 nvcc flags, :225 `-DFA3_LIB_NAME`, :186-200 `-l
 defines `torch.utils.cpp_extension.load` adds.  No reference source is copied into this repository;
 only the built `.so` lands under `oracle/_ref/` (git-ignored).
 
-The `.so` needs a GPU to run.  It is used by `bench.py` (optional A/B timing of the reference kernel on
-the same tensors) and by GPU tests that compare our error against the reference kernel's own error.
+The `.so` needs a GPU to run.  It is used by `bench.py --impl reference-kernel` (optional A/B timing of the
+reference's kernel against ours on the same tensors) and by nothing else.
+
+The reference checkout is found through `--ref`, the environment variable FA_REFERENCE_ROOT, or a directory named
+`reference` beside this repository.
 
 Usage:  python oracle/build_ref.py [--ref /path/to/reference] [--force]
 """
@@ -25,8 +28,14 @@ OUT_SO = os.path.join(OUT_DIR, "fa4_ref.so")
 NAMESPACE = "fa4_ref"
 
 
-def build(ref_root: str = "/root/reference", force: bool = False, verbose: bool = True) -> str | None:
+def default_ref_root() -> str:
+    env = os.environ.get("FA_REFERENCE_ROOT")
+    return env if env else os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(ref_root: str | None = None, force: bool = False, verbose: bool = True) -> str | None:
     """Returns the path of the built library, or None when the reference checkout is absent."""
+    ref_root = ref_root or default_ref_root()
     src = os.path.join(ref_root, "kernels", "fa4_blackwell.cu")
     if not os.path.isfile(src):
         return OUT_SO if os.path.isfile(OUT_SO) else None
@@ -60,7 +69,7 @@ def build(ref_root: str = "/root/reference", force: bool = False, verbose: bool 
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=None, help="reference checkout (default: $FA_REFERENCE_ROOT or ../reference)")
     ap.add_argument("--force", action="store_true")
     a = ap.parse_args()
     p = build(a.ref, a.force)

@@ -80,7 +80,7 @@ class Plan:
 def prefill_tc_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> bool:
     if q_dtype != kv_dtype:
         return False
-    if (hd, hdv) not in ((64, 64), (96, 96), (128, 128), (192, 128)):
+    if (hd, hdv) not in ((64, 64), (96, 96), (128, 128), (192, 128), (256, 256), (192, 192)):
         return False
     if q_dtype == DT_FP8 and (hd, hdv) != (128, 128):
         return False
@@ -121,7 +121,8 @@ def make_plan(*, batch, max_seqlen_q, max_seqlen_k, hq, hkv, hd, hdv, q_dtype=DT
         else:
             route = ROUTE_GENERAL
     if route == ROUTE_PREFILL_TC:
-        tile_m, tile_n, rpt = 256, 128, 1
+        # one 128-row tile per work item where the O accumulator (hdv > 128 columns) leaves TMEM no room for two
+        tile_m, tile_n, rpt = (128 if (hd, hdv) in ((256, 256), (192, 192)) else 256), 128, 1
     elif route == ROUTE_DECODE:
         tile_m, tile_n, rpt = 16, 64, rep
     else:

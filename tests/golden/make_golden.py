@@ -2,7 +2,7 @@
 
 Run in a checkout that has the reference mounted (it is imported, never copied):
 
-    python tests/golden/make_golden.py --ref /root/reference
+    python tests/golden/make_golden.py --ref <reference checkout>
 
 For each small scenario below it calls the reference's `make_inputs(cfg, seed, device="cpu")`
 (bench/scenarios.py:741-819) and its fp32 oracle `ref_fp32` (bench/scenarios.py:943-1024) and stores
@@ -69,7 +69,7 @@ def scenarios(S):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", required=True, help="path of the reference checkout (read-only)")
     a = ap.parse_args()
     sys.path.insert(0, a.ref)
     from bench import scenarios as S  # the reference's module, imported from where it lies

@@ -148,14 +148,15 @@ def test_decode_route_with_several_row_tiles(hq, hkv, q_lens, kv_dtype, cuda_dev
     _check(out, lse, ref_out, ref_lse, _tol(p.q, p.k), "decode_tiles/auto")
 
 
-@pytest.mark.parametrize("page_size", [16, 32, 128, 192, 256])
-def test_decode_route_page_sizes(page_size, cuda_device):
+@pytest.mark.parametrize("kv_dtype", [None, "fp8"])
+@pytest.mark.parametrize("page_size", [16, 32, 128, 192, 256, 320])
+def test_decode_route_page_sizes(page_size, kv_dtype, cuda_device):
     p = W.make_problem("decode_pages", [(1, 1000), (2, 257), (1, 64), (1, 3)], hq=8, hkv=2, hd=128, causal=True,
-                       page_size=page_size, leftpad=[9, 0, 0, 1], seed=31)
+                       page_size=page_size, leftpad=[9, 0, 0, 1], kv_dtype=kv_dtype, seed=31)
     ref_out, ref_lse = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
     pd = p.to(cuda_device)
     out, lse, _ = capi.fwd(pd.q, pd.k, pd.v, route=capi.FA_ROUTE_DECODE, check=True, **pd.capi_kw())
-    _check(out, lse, ref_out, ref_lse, 2e-2, f"decode_pages/{page_size}")
+    _check(out, lse, ref_out, ref_lse, _tol(p.q, p.k), f"decode_pages/{page_size}/{kv_dtype}")
 
 
 def test_small_shapes_of_benchmark_configs(cuda_device):

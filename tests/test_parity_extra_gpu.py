@@ -171,6 +171,19 @@ def test_e4m3_prefill_full_tensor_error_has_margin(cuda_device):
     assert worst <= 4.5e-2
 
 
+@pytest.mark.parametrize("page_size", [0, 64])
+def test_mixed_decode_and_prefill_batch(page_size, cuda_device):
+    """Decode-shaped sequences (1-2 new tokens) and prefill-shaped ones in one call: the library splits the batch
+    between the decode kernel and the tensor-core prefill kernel (two work lists, one call); the result must not
+    depend on which kernel took which sequence."""
+    reqs = [(1, 900), (1, 300), (700, 700), (1, 64), (2, 1500), (300, 1200), (1, 1), (0, 40)]
+    p = W.make_problem(f"mixed_p{page_size}", reqs, hq=8, hkv=2, hd=128, causal=True, page_size=page_size,
+                       leftpad=[3, 0, 0, 10, 0, 100, 0, 0] if page_size else None, sink=True, seed=56)
+    assert p.q.shape[0] * 4 < len(reqs) * p.max_seqlen_q        # ragged enough for the split to be chosen
+    _check(p, cuda_device, AUTO, 2e-2)
+    _check(p, cuda_device, TC, 2e-2)                            # forced: the prefill kernel alone gives the same
+
+
 # ---------------------------------------------------------------------------------------------------------
 # scheduler metadata
 # ---------------------------------------------------------------------------------------------------------
