@@ -34,8 +34,8 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 # DRAM traffic per launch measured once with ncu (dram__bytes_read.sum + dram__bytes_write.sum); the captures and
-# their commands are summarised under profiles/.  Prefill was captured at B=2 (133.2 MB) and grows in proportion to B.
-NCU_PREFILL_TRAFFIC_PER_BATCH = 66.6e6
+# their commands are summarised under profiles/.  Prefill was captured at B=2 (137.6 MB) and grows in proportion to B.
+NCU_PREFILL_TRAFFIC_PER_BATCH = 68.8e6
 NCU_DECODE_TRAFFIC = {"bf16": 8.59e9, "fp8": 4.307e9}
 METRIC = "prefill TFLOP/s per job (causal GQA bf16 B=4 Hq=32 Hkv=8 S=4096 d=128); decode HBM GB/s in `decode`"
 L2_BYTES = 126 * 1024 * 1024
