@@ -59,7 +59,8 @@ struct TcArgs {
   int item_rows;     // query rows per work item: 256 (two tiles) or 128 (one tile: head dims whose O needs > 128 columns)
   int use_list;      // kp.work holds scheduler metadata of this route: items = its valid entries x hq
   int stage_out;     // map_o is valid: full 32-row groups leave through shared memory and TMA stores
-  int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128)
+  int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128); 1 in gather mode
+  int gather;        // pages of 1, 2 or 4 keys: K/V maps are 2-D with one-row boxes, rows come four per tile::gather4
   int kv_total_rows; // rows of the K/V tensor map (out-of-range y => zero fill)
   int out_cols;      // value columns that exist (head_dim 96 runs as 128 with zero-filled columns 96..127)
 };
@@ -165,18 +166,36 @@ struct Ring {
   }
 };
 
-// One K or V tile of a PAGED cache: one TMA box per page (or per 128 keys of a larger page), each after its
-// page-table lookup.  Kept out of line and rolled on purpose: the producer thread shares its instruction cache with
-// the softmax warps, whose loop bodies are large, and the time of this path went with its code size (a fully
-// unrolled form with the lookups hoisted measured 372 TFLOP/s on pages of 16 keys, the rolled inline form 583).
+// One K or V tile of a PAGED cache, loaded by the whole producer warp: lane j owns TMA box j of the tile (one page, or
+// 128 keys of a larger page) and looks its page up itself; with pages of 1, 2 or 4 keys lane g owns keys 4g .. 4g+3 and
+// fetches them with one tile::gather4 per 128-byte column block (2-D maps over [rows][heads x head_dim] then).
+// Kept out of line and rolled on purpose: the producer shares its instruction cache with the softmax warps, whose
+// loop bodies are large, and the time of this path went with its code size (a fully unrolled single-thread form
+// measured 372 TFLOP/s on pages of 16 keys, the rolled inline form 583).
 template <int EPB>
 __device__ __noinline__ void load_tile_paged(const TcArgs& a, const CUtensorMap* map, int width, uint32_t dst, int nb,
-                                             uint32_t bar, int b, int seqlen_k, int hk) {
+                                             uint32_t bar, int b, int seqlen_k, int hk, int lane) {
   const KParams& p = a.kp;
   const int32_t* pt = p.page_table + (int64_t)b * p.page_table_stride;
   const int ncb = width / EPB;
+  if (a.gather) {
+    int y[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int kk = nb * TN + 4 * lane + j;
+      y[j] = 0;                  // beyond the sequence: pool row 0 (finite by contract), masked by the softmax
+      if (kk < seqlen_k) {
+        const int lp = kk >> p.page_shift;
+        y[j] = (pt[lp] << p.page_shift) + (kk - (lp << p.page_shift));
+      }
+    }
 #pragma unroll 1
-  for (int r = 0; r < TN; r += a.kv_box_rows) {
+    for (int cb = 0; cb < ncb; ++cb)
+      tma_gather4_2d(dst + cb * (TN * 128) + lane * 512, map, hk * width + cb * EPB, y[0], y[1], y[2], y[3], bar);
+    return;
+  }
+  const int r = lane * a.kv_box_rows;
+  if (r < TN) {
     const int kk = nb * TN + r;
     int y = a.kv_total_rows;   // beyond the sequence: out of range => zeros
     if (kk < seqlen_k) {
@@ -267,7 +286,12 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
   asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
   if (warp == WARP_TMA) {
     // =========================================== TMA producer ===========================================
-    if (lane == 0) {
+    // The whole warp runs the control flow; lane 0 (the leader) waits on the barriers, takes work ids, issues the Q
+    // copies and the copies of unpaged K/V tiles; every wait's outcome and every decoded item is broadcast, and for
+    // paged tiles all lanes look pages up and issue copies (load_tile_paged).
+    {
+      constexpr uint32_t FULLM = 0xffffffffu;
+      const bool leader = lane == 0;
       uint32_t qcnt = 0, k0cnt = 0;
       Ring<KST> kr;
       Ring<VST> vr;
@@ -280,37 +304,48 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         if (sched_header_matches(p.work, p.work_expect)) {
           num_items = p.work[6] * p.hq;
         } else {
-          report_error(p.status, DEV_ERR_BAD_INDEX, ROLE_TMA);
+          if (leader) report_error(p.status, DEV_ERR_BAD_INDEX, ROLE_TMA);
           num_items = 0;
         }
       }
       bool first_ticket = true;
+      auto lead_wait = [&](uint32_t bar, uint32_t parity) -> bool {
+        int r = 1;
+        if (leader) r = wait_or_abort(bar, parity, s_abort) ? 1 : 0;
+        return __shfl_sync(FULLM, r, 0) != 0;
+      };
       // work items are handed out heaviest first: a CTA's first id is its block index, later ones come from one
       // global counter; every role of this CTA learns the item from a two-slot mailbox in shared memory
       auto fetch_and_publish = [&]() -> Item {
-        Item it;
-        it.w = kEndOfWork;
+        Item it{0, 0, 0, 0, 0, 0, 0, 0, {0, 0}, {0, 0}, 0, 0, 0, kEndOfWork};
         const uint32_t slot = wcnt & 1;
-        if (!wait_or_abort(bar_w_empty + 8 * slot, ((wcnt >> 1) & 1) ^ 1, s_abort)) {
-          report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA);
+        if (!lead_wait(bar_w_empty + 8 * slot, ((wcnt >> 1) & 1) ^ 1)) {
+          if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA);
           ok = false;
           return it;
         }
-        // ids whose (batch, tile) owns no query row (ragged batches) are dropped here, without a hand-off
-        while (true) {
-          const int w = first_ticket ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(p.counters, 1);
-          first_ticket = false;
-          if (w >= num_items) { it.w = kEndOfWork; break; }
-          bool bad = false;
-          it = decode_item<NTL>(a, w, &bad);   // sequence bounds are read from global memory once per item
-          if (bad) { report_error(p.status, DEV_ERR_BAD_INDEX, ROLE_TMA); num_items = 0; it.w = kEndOfWork; break; }
-          if (it.valid) break;
-        }
-        const int4* src = reinterpret_cast<const int4*>(&it);
-        int4* dst = reinterpret_cast<int4*>(&s_item[slot]);
+        if (leader) {
+          // ids whose (batch, tile) owns no query row (ragged batches) are dropped here, without a hand-off
+          while (true) {
+            const int w = first_ticket ? (int)blockIdx.x : (int)gridDim.x + atomicAdd(p.counters, 1);
+            first_ticket = false;
+            if (w >= num_items) { it.w = kEndOfWork; break; }
+            bool bad = false;
+            it = decode_item<NTL>(a, w, &bad);   // sequence bounds are read from global memory once per item
+            if (bad) { report_error(p.status, DEV_ERR_BAD_INDEX, ROLE_TMA); num_items = 0; it.w = kEndOfWork; break; }
+            if (it.valid) break;
+          }
+          const int4* src = reinterpret_cast<const int4*>(&it);
+          int4* dst = reinterpret_cast<int4*>(&s_item[slot]);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) dst[i] = src[i];
-        mbar_arrive(bar_w_full + 8 * slot);   // release: the slot is visible to whoever observes the phase
+          for (int i = 0; i < 4; ++i) dst[i] = src[i];
+          mbar_arrive(bar_w_full + 8 * slot);   // release: the slot is visible to whoever observes the phase
+        }
+        {
+          int* pi = reinterpret_cast<int*>(&it);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pi[i] = __shfl_sync(FULLM, pi[i], 0);
+        }
         ++wcnt;
         return it;
       };
@@ -324,78 +359,84 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         // (causal masking), so its Q slot is free, and refilled, a block earlier; the next item's first loads are
         // then spread over two blocks instead of one.  Order: Q tile 0, K of the first block, Q tile 1.
         auto load_q = [&](int t) -> bool {
-          if (!wait_or_abort(bar_q_empty + 8 * t, (qcnt & 1) ^ 1, s_abort)) return false;
-          mbar_expect_tx(bar_q_full + 8 * t, TM * HD * ESZ);
+          if (!lead_wait(bar_q_empty + 8 * t, (qcnt & 1) ^ 1)) return false;
+          if (leader) {
+            mbar_expect_tx(bar_q_full + 8 * t, TM * HD * ESZ);
 #pragma unroll
-          for (int cb = 0; cb < HD / EPB; ++cb)
-            tma_load_3d(sQ + t * (TM * HD * ESZ) + cb * (TM * 128), &map_q, cb * EPB, it.h,
-                        it.q0 + it.pair * (NTL * TM) + t * TM, bar_q_full + 8 * t);
+            for (int cb = 0; cb < HD / EPB; ++cb)
+              tma_load_3d(sQ + t * (TM * HD * ESZ) + cb * (TM * 128), &map_q, cb * EPB, it.h,
+                          it.q0 + it.pair * (NTL * TM) + t * TM, bar_q_full + 8 * t);
+          }
           return true;
         };
         ok = load_q(0);
-        if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+        if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
         const int hk = it.h / p.rep;
         // one K or V tile of key block nb into `dst`, completing on `bar`
         auto load_tile = [&](const CUtensorMap* map, int width, uint32_t dst, int nb, uint32_t bar) {
           if (p.page_table == nullptr) {
-            for (int cb = 0; cb < width / EPB; ++cb)
-              tma_load_3d(dst + cb * (TN * 128), map, cb * EPB, hk, it.k0 + nb * TN, bar);
+            if (leader) {
+              for (int cb = 0; cb < width / EPB; ++cb)
+                tma_load_3d(dst + cb * (TN * 128), map, cb * EPB, hk, it.k0 + nb * TN, bar);
+            }
           } else {
-            load_tile_paged<EPB>(a, map, width, dst, nb, bar, it.b, it.seqlen_k, hk);
+            load_tile_paged<EPB>(a, map, width, dst, nb, bar, it.b, it.seqlen_k, hk, lane);
           }
         };
         // K of the first block has a barrier of its own; every later K tile arrives together with the V tile of
         // the block before it (the MMA warp needs both at the same point), so the consumer waits once per block
         {
           const uint32_t s = kr.slot;
-          ok = wait_or_abort(bar_k_empty + 8 * s, kr.phase ^ 1u, s_abort);
-          if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+          ok = lead_wait(bar_k_empty + 8 * s, kr.phase ^ 1u);
+          if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
           const uint32_t kbar = MERGE_KV ? bar_k0_full : bar_k_full + 8 * s;
-          mbar_expect_tx(kbar, SM::kKStage);
+          if (leader) mbar_expect_tx(kbar, SM::kKStage);
           load_tile(&map_k, HD, sK + s * SM::kKStage, it.ulo, kbar);
           kr.advance();
           ++k0cnt;
         }
         if constexpr (NTL == 2) {
           ok = load_q(1);
-          if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+          if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
         }
         ++qcnt;
         for (int nb = it.ulo; nb < it.uhi; ++nb) {
           const bool nxt = nb + 1 < it.uhi;
           const uint32_t vs = vr.slot, ks = kr.slot;
-          ok = wait_or_abort(bar_v_empty + 8 * vs, vr.phase ^ 1u, s_abort);
-          if (ok && nxt) ok = wait_or_abort(bar_k_empty + 8 * ks, kr.phase ^ 1u, s_abort);
-          if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
-          mbar_expect_tx(bar_v_full + 8 * vs, SM::kVStage + ((MERGE_KV && nxt) ? SM::kKStage : 0));
+          ok = lead_wait(bar_v_empty + 8 * vs, vr.phase ^ 1u);
+          if (ok && nxt) ok = lead_wait(bar_k_empty + 8 * ks, kr.phase ^ 1u);
+          if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+          if (leader) mbar_expect_tx(bar_v_full + 8 * vs, SM::kVStage + ((MERGE_KV && nxt) ? SM::kKStage : 0));
           load_tile(&map_v, HDV, sV + vs * SM::kVStage, nb, bar_v_full + 8 * vs);
           vr.advance();
           if (nxt) {
             const uint32_t kbar = MERGE_KV ? bar_v_full + 8 * vs : bar_k_full + 8 * ks;
-            if constexpr (!MERGE_KV) mbar_expect_tx(kbar, SM::kKStage);
+            if constexpr (!MERGE_KV) { if (leader) mbar_expect_tx(kbar, SM::kKStage); }
             load_tile(&map_k, HD, sK + ks * SM::kKStage, nb + 1, kbar);
             kr.advance();
           }
           if (nb == it.ulo) it_next = fetch_and_publish();
         }
       }
-      if (!ok) *s_abort = 1;
-      // drain: every copy this thread issued must have landed before the CTA may leave
-      if (qcnt > 0) {
-        wait_or_abort(bar_q_full, (qcnt - 1) & 1, s_abort + 1 /* never set: pure time limit */);
-        if constexpr (NTL == 2) wait_or_abort(bar_q_full + 8, (qcnt - 1) & 1, s_abort + 1);
-      }
-      if constexpr (MERGE_KV) {
-        if (k0cnt > 0) wait_or_abort(bar_k0_full, (k0cnt - 1) & 1, s_abort + 1);
-      } else {
-        for (uint32_t s = 0; s < (uint32_t)KST; ++s) {
-          if (kr.n > s) { const uint32_t last = (kr.n - 1 - s) / KST; wait_or_abort(bar_k_full + 8 * s, last & 1, s_abort + 1); }
+      if (!ok && leader) *s_abort = 1;
+      // drain: every copy this warp issued must have landed before the CTA may leave
+      if (leader) {
+        if (qcnt > 0) {
+          wait_or_abort(bar_q_full, (qcnt - 1) & 1, s_abort + 1 /* never set: pure time limit */);
+          if constexpr (NTL == 2) wait_or_abort(bar_q_full + 8, (qcnt - 1) & 1, s_abort + 1);
         }
+        if constexpr (MERGE_KV) {
+          if (k0cnt > 0) wait_or_abort(bar_k0_full, (k0cnt - 1) & 1, s_abort + 1);
+        } else {
+          for (uint32_t s = 0; s < (uint32_t)KST; ++s) {
+            if (kr.n > s) { const uint32_t last = (kr.n - 1 - s) / KST; wait_or_abort(bar_k_full + 8 * s, last & 1, s_abort + 1); }
+          }
+        }
+        for (uint32_t s = 0; s < (uint32_t)VST; ++s) {
+          if (vr.n > s) { const uint32_t last = (vr.n - 1 - s) / VST; wait_or_abort(bar_v_full + 8 * s, last & 1, s_abort + 1); }
+        }
+        counters_release(p.counters);   // this CTA takes no more tickets
       }
-      for (uint32_t s = 0; s < (uint32_t)VST; ++s) {
-        if (vr.n > s) { const uint32_t last = (vr.n - 1 - s) / VST; wait_or_abort(bar_v_full + 8 * s, last & 1, s_abort + 1); }
-      }
-      counters_release(p.counters);   // this CTA takes no more tickets
     }
   } else if (warp == WARP_MMA) {
     // =========================================== MMA issuer =============================================
@@ -1018,9 +1059,9 @@ struct MapCache {
 };
 
 static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t rows, uint64_t heads, uint64_t head_dim,
-                        uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_rows) {
+                        uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_rows, int rank = 3) {
   static thread_local MapCache cache;
-  const MapKey k{ptr, rows, heads, head_dim, head_stride_elems, row_stride_elems, box_rows, dtype};
+  const MapKey k{ptr, rows, heads, head_dim, head_stride_elems, row_stride_elems, box_rows, dtype + 16 * rank};
   for (int i = 0; i < MapCache::N; ++i)
     if (cache.used[i] && cache.key[i] == k) { *m = cache.map[i]; return true; }
   EncodeTiledFn fn = get_encode_fn();
@@ -1033,10 +1074,20 @@ static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t row
   const CUtensorMapDataType dt = dtype == FA_DT_FP8_E4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : dtype == FA_DT_FP16   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  if (fn(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return false;
+  bool good;
+  if (rank == 2) {     // [rows][columns], columns innermost
+    const cuuint64_t dims2[2] = {head_dim, rows};
+    const cuuint64_t strides2[1] = {row_stride_elems * esz};
+    const cuuint32_t box2[2] = {128 / esz, box_rows};
+    good = fn(m, dt, 2, const_cast<void*>(ptr), dims2, strides2, box2, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  } else {
+    good = fn(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  }
+  if (!good) return false;
   const int slot = cache.next;
   cache.next = (cache.next + 1) % MapCache::N;
   cache.key[slot] = k;
@@ -1055,13 +1106,21 @@ static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
   a.num_items = kp.batch * kp.hq * a.max_pairs;
   a.use_list = kp.work != nullptr;
   const bool paged = kp.page_table != nullptr;
-  a.kv_box_rows = paged ? (kp.page_size < TN ? kp.page_size : TN) : TN;
+  a.gather = paged && (kp.page_size == 1 || kp.page_size == 2 || kp.page_size == 4);
+  a.kv_box_rows = a.gather ? 1 : (paged ? (kp.page_size < TN ? kp.page_size : TN) : TN);
   a.kv_total_rows = (int)kv_rows;
   a.out_cols = kp.hdv;
   CUtensorMap mq, mk, mv, mo;
   if (!make_map_3d(&mq, kp.q, dtype, (uint64_t)kp.total_q, kp.hq, kp.hd, kp.hd, (uint64_t)kp.q_row_stride, TM)) return -1;
-  if (!make_map_3d(&mk, kp.k, dtype, kv_rows, kp.hkv, kp.hd, kp.hd, (uint64_t)kp.k_row_stride, a.kv_box_rows)) return -1;
-  if (!make_map_3d(&mv, kp.v, dtype, kv_rows, kp.hkv, kp.hdv, kp.hdv, (uint64_t)kp.v_row_stride, a.kv_box_rows)) return -1;
+  if (a.gather) {
+    // 2-D views [rows][hkv * head_dim] with one-row boxes (tile::gather4 wants a 2-D map whose box has one row):
+    // expressed through the 3-D encoder as one "head" of hkv * head_dim columns
+    if (!make_map_3d(&mk, kp.k, dtype, kv_rows, 1, (uint64_t)kp.hkv * kp.hd, (uint64_t)kp.hkv * kp.hd, (uint64_t)kp.k_row_stride, 1, 2)) return -1;
+    if (!make_map_3d(&mv, kp.v, dtype, kv_rows, 1, (uint64_t)kp.hkv * kp.hdv, (uint64_t)kp.hkv * kp.hdv, (uint64_t)kp.v_row_stride, 1, 2)) return -1;
+  } else {
+    if (!make_map_3d(&mk, kp.k, dtype, kv_rows, kp.hkv, kp.hd, kp.hd, (uint64_t)kp.k_row_stride, a.kv_box_rows)) return -1;
+    if (!make_map_3d(&mv, kp.v, dtype, kv_rows, kp.hkv, kp.hdv, kp.hdv, (uint64_t)kp.v_row_stride, a.kv_box_rows)) return -1;
+  }
   // output map (16-bit element type of the output): 64 columns x 32 rows per store.  A layout TMA cannot describe
   // only switches the staged path off.
   a.stage_out = 0;
@@ -1105,7 +1164,8 @@ bool prefill_tc_supported(const PlanInput& in) {
   if (in.q_dtype == FA_DT_FP8_E4M3 && !(in.hd == 128 && in.hdv == 128)) return false;   // e4m3: head_dim 128 only
   if (in.page_size > 0) {
     const int ps = in.page_size;
-    if (ps % 8 != 0 || !((128 % ps == 0) || (ps % 128 == 0))) return false;
+    const bool gather = (ps == 1 || ps == 2 || ps == 4) && in.hd != 96;   // four rows per tile::gather4 (2-D maps: no zero-filled columns)
+    if (!gather && (ps % 8 != 0 || !((128 % ps == 0) || (ps % 128 == 0)))) return false;
   }
   return in.hkv > 0 && in.hq % in.hkv == 0;
 }

@@ -108,11 +108,12 @@ def test_decode_route_gathers_small_pages(page_size, kv_dtype, cuda_device):
     _check(p, cuda_device, AUTO, tol)
 
 
-@pytest.mark.parametrize("page_size", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("page_size", [1, 2, 4, 8, 16, 32, 64, 128, 256])
 @pytest.mark.parametrize("dtype", ["bf16", "fp8"])
 def test_tensor_core_prefill_over_pages(page_size, dtype, cuda_device):
-    """The tcgen05 prefill kernel forced onto paged KV: pages that divide a 128-key tile and pages that hold
-    one or two whole tiles; ragged lengths, a chunk (q_len < k_len) and leftpad."""
+    """The tcgen05 prefill kernel forced onto paged KV: pages of 1, 2, 4 keys (rows gathered four at a time), pages
+    that divide a 128-key tile and pages that hold one or two whole tiles; ragged lengths, a chunk (q_len < k_len)
+    and leftpad."""
     p = W.make_problem(f"tc_pages_{dtype}_{page_size}", [(300, 300), (130, 700), (256, 257), (5, 1000)], hq=4, hkv=2,
                        hd=128, dtype=dtype, causal=True, page_size=page_size, leftpad=[0, 70, 0, 129], seed=43)
     _check(p, cuda_device, TC, 6e-2 if dtype == "fp8" else 2e-2)
