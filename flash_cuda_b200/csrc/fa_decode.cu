@@ -8,7 +8,8 @@
 //   warp 4      producer: resolves page-table entries (32 at a time, one coalesced load) and streams whole
 //               pages with TMA 2-D boxes over the page pool viewed as [num_pages * page_size, hkv * hd] into a
 //               ring of 32 KB stages (64 keys of 16-bit K+V, or 128 keys of e4m3 K+V; 128-byte swizzle).  The ring runs on across
-//               work-item boundaries; each stage carries a small descriptor (work id, first key, flags).
+//               work-item boundaries; each stage carries a small descriptor (work id, first key, flags).  Pages
+//               of 1, 2 or 4 keys are fetched with cp.async, 16 bytes per lane, into the same swizzled layout.
 //   warps 0-3   consumers: each takes a quarter of the stage's keys: S = Q K^T and O += P V with warp-level
 //               MMA (ldmatrix from the swizzled stage), a private online softmax, and at the end of the work
 //               item a cross-warp merge through shared memory.
@@ -45,7 +46,7 @@ struct DecArgs {
   int total_work;     // num_work * hkv * nsplits
   int box_rows;       // rows per TMA box = min(page_size, 64); 1 in gather mode
   int kv_total_rows;
-  int gather;         // pages of 1, 2 or 4 keys: rows are fetched four at a time with tile::gather4
+  int gather;         // pages of 1, 2 or 4 keys: rows are fetched 16 bytes per lane with cp.async
 };
 
 template <int ESZ, int NST, int HD, int HDV, int TNS_>
@@ -103,6 +104,60 @@ __device__ __forceinline__ WorkItem decode_work(const KParams& p, int w) {
   return it;
 }
 
+// The cp.async producer's copies of one operand (K or V) of a stage: TNS rows of CPR 16-byte chunks, row r from
+// pool row yr[r / 32] of lane r % 32, written where a 128-byte-swizzled TMA box would have put them (column block
+// ch / 8 of the stage, row r, chunk (ch % 8) ^ (r % 8)).
+template <int CPR, int TNS>
+__device__ __forceinline__ void copy_rows(uint32_t dst0, const unsigned char* src0, uint32_t pitch,
+                                          const int (&yr)[TNS / 32], int lane) {
+  if constexpr (32 % CPR == 0) {
+    // RPI rows per instruction; row r = i * RPI + hb, and (r & 7) = ((i * RPI) & 7) ^ hb because the low bits of
+    // i * RPI are clear: the swizzle term splits into a lane constant and an immediate
+    constexpr int RPI = 32 / CPR;
+    const int hb = lane / CPR, ch = lane - hb * CPR;
+    const uint32_t dl = dst0 + (uint32_t)(ch >> 3) * (TNS * 128) + (uint32_t)hb * 128u;
+    const uint32_t xs = (uint32_t)(((ch & 7) ^ hb) << 4);
+    const unsigned char* sl = src0 + ch * 16;
+    // the row numbers of eight copies are fetched first: a shuffle followed at once by its copy would cost the
+    // shuffle's latency per copy (the statements are not reordered)
+    constexpr int G = 8;
+    static_assert((TNS / RPI) % G == 0, "whole groups");
+#pragma unroll
+    for (int i0 = 0; i0 < TNS / RPI; i0 += G) {
+      int y[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const int i = i0 + g;
+        y[g] = __shfl_sync(0xffffffffu, yr[(i * RPI) >> 5], ((i * RPI) & 31) + hb);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const int i = i0 + g;
+        cp_async16(dl + (uint32_t)(i * RPI) * 128u + (xs ^ (uint32_t)(((i * RPI) & 7) << 4)),
+                   sl + (uint64_t)(uint32_t)y[g] * pitch, 16u);
+      }
+    }
+  } else {
+    constexpr int N = TNS * CPR / 32, G = 8;
+    static_assert(N % G == 0, "whole groups");
+#pragma unroll
+    for (int i0 = 0; i0 < N; i0 += G) {
+      int y[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const int i = i0 + g, r = (i * 32 + lane) / CPR;
+        y[g] = __shfl_sync(0xffffffffu, yr[(i * 32 / CPR) >> 5], r & 31);
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const int q = (i0 + g) * 32 + lane, r = q / CPR, ch = q - r * CPR;
+        cp_async16(dst0 + (uint32_t)(ch >> 3) * (TNS * 128) + (uint32_t)r * 128u + (uint32_t)(((ch & 7) ^ (r & 7)) << 4),
+                   src0 + (uint64_t)(uint32_t)y[g] * pitch + ch * 16, 16u);
+      }
+    }
+  }
+}
+
 // T = MMA element type (bf16 / fp16); KV8 = the cache holds e4m3 bytes.
 template <typename T, bool KV8, int NST, int HD, int HDV, int CPS, int TNS_>
 __global__ void __launch_bounds__((ncons_for(KV8 ? 1 : 2) + 1) * 32, CPS)
@@ -137,7 +192,9 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
-    for (int s = 0; s < NST; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, NC); }
+    // cp.async stages complete on 33 arrivals: one per producer lane when its copies have landed, one from lane 0
+    // after it has written the stage's descriptor
+    for (int s = 0; s < NST; ++s) { mbar_init(bar_full + 8 * s, a.gather ? 33 : 1); mbar_init(bar_empty + 8 * s, NC); }
     s_abort[0] = 0; s_abort[1] = 0;
     mbar_fence_init();
   }
@@ -158,6 +215,11 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
       total_work = 0;
     }
     bool first_ticket = true;
+    // a stage that carries no copies: lane 0 has written its descriptor
+    auto publish_plain = [&](uint32_t s) {
+      if (a.gather) mbar_arrive(bar_full + 8 * s);
+      if (lane == 0) mbar_arrive(bar_full + 8 * s);
+    };
     while (ok) {
       int w = 0;
       if (first_ticket) w = (int)blockIdx.x;     // a CTA's first work id is its block index, later ones are tickets
@@ -175,10 +237,8 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
         const uint32_t s = cnt % NST;
         ok = wait_or_abort(bar_empty + 8 * s, ((cnt / NST) & 1) ^ 1, s_abort);
         if (!ok) break;
-        if (lane == 0) {
-          s_info[4 * s] = w; s_info[4 * s + 1] = 0; s_info[4 * s + 2] = F_FIRST | F_LAST | F_EMPTY;
-          mbar_arrive(bar_full + 8 * s);
-        }
+        if (lane == 0) { s_info[4 * s] = w; s_info[4 * s + 1] = 0; s_info[4 * s + 2] = F_FIRST | F_LAST | F_EMPTY; }
+        publish_plain(s);
         ++cnt;
         continue;
       }
@@ -186,27 +246,36 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
       int cache_first = -1, cache_id = 0;       // 32 page-table entries, one per lane
       const int key_end = it.hi * TN;
       if (a.gather) {
-        // Pages smaller than a TMA box: lane g < 16 owns keys 4g..4g+3 of every stage, looks their physical rows up
-        // itself (before it waits for the stage, so that the lookups overlap the wait) and issues one gather4 per
-        // 128-byte column block of K and V.  Keys beyond the sequence fetch pool row 0 and are masked by the consumers.
+        // Pages of 1, 2 or 4 keys, 16 bytes per lane: lane g looks up the physical rows of keys g, g + 32, .. of
+        // a stage (one stage ahead, so that the lookups are in flight while the current stage is issued), then the
+        // warp walks the stage's 16-byte chunks in row order, CPR consecutive lanes on one row, and writes them
+        // where the swizzled TMA box would have put them.  The TMA unit retires about one copy per 100 cycles
+        // whatever its size; these copies go through the load/store path instead (the reference's route for page
+        // size 1, kernels/fa4_blackwell.cu:8936-8947).  Keys beyond the sequence fetch pool row 0 and are masked
+        // by the consumers.
         const int32_t* pt = p.page_table + (int64_t)it.b * p.page_table_stride;
-        for (int key0 = it.lo * TN; key0 < key_end && ok; key0 += TNS) {
-          // copy o of the stage = (group o >> 1 of four keys, K or V by o & 1); the lanes take copies o = lane, lane + 32, ..
-          constexpr int NGO = (TNS / 4) * 2, OPL = (NGO + 31) / 32;
-          int y[OPL][4];
+        constexpr int RG = TNS / 32;
+        auto lookup = [&](int key0, int (&yr)[RG]) {
 #pragma unroll
-          for (int u = 0; u < OPL; ++u) {
-            const int grp = (lane + 32 * u) >> 1;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const int kk = key0 + 4 * grp + j;
-              y[u][j] = 0;
-              if (lane + 32 * u < NGO && kk < it.seqlen_k && kk < key_end) {
-                const int lp = kk >> p.page_shift;          // gather mode: the page size is 1, 2 or 4
-                y[u][j] = (pt[lp] << p.page_shift) + (kk - (lp << p.page_shift));
-              }
+          for (int u = 0; u < RG; ++u) {
+            const int kk = key0 + 32 * u + lane;
+            yr[u] = 0;
+            if (kk < it.seqlen_k && kk < key_end) {
+              const int lp = kk >> p.page_shift;
+              yr[u] = (pt[lp] << p.page_shift) + (kk - (lp << p.page_shift));
             }
           }
+        };
+        const unsigned char* kb = reinterpret_cast<const unsigned char*>(p.k) + (int64_t)it.hk * HD * ESZ;
+        const unsigned char* vb = reinterpret_cast<const unsigned char*>(p.v) + (int64_t)it.hk * HDV * ESZ;
+        const uint32_t kpitch = (uint32_t)(p.k_row_stride * ESZ), vpitch = (uint32_t)(p.v_row_stride * ESZ);
+        int ynext[RG];
+        lookup(it.lo * TN, ynext);
+        for (int key0 = it.lo * TN; key0 < key_end && ok; key0 += TNS) {
+          int ycur[RG];
+#pragma unroll
+          for (int u = 0; u < RG; ++u) ycur[u] = ynext[u];
+          if (key0 + TNS < key_end) lookup(key0 + TNS, ynext);
           const uint32_t s = cnt % NST;
           ok = wait_or_abort(bar_empty + 8 * s, ((cnt / NST) & 1) ^ 1, s_abort);
           if (!ok) break;
@@ -216,23 +285,11 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
             if (key0 == it.lo * TN) flags |= F_FIRST;
             if (key0 + TNS >= key_end) flags |= F_LAST;
             s_info[4 * s] = w; s_info[4 * s + 1] = key0; s_info[4 * s + 2] = flags;
-            mbar_expect_tx(bar_full + 8 * s, SM::kStage);
+            mbar_arrive(bar_full + 8 * s);
           }
-#pragma unroll
-          for (int u = 0; u < OPL; ++u) {
-            const int o = lane + 32 * u;
-            if (o < NGO) {
-              const uint32_t roff = (uint32_t)(4 * (o >> 1)) * 128u;
-              const bool is_v = (o & 1) != 0;
-              const uint32_t dst = (is_v ? vdst : kdst) + roff;
-              const CUtensorMap* map = is_v ? &map_v : &map_k;
-              const int x0 = it.hk * (is_v ? HDV : HD);
-              constexpr int EPB = KV8 ? 128 : 64;           // elements per 128-byte column block
-              const int ncb = (is_v ? HDV : HD) / EPB;
-              for (int cb = 0; cb < ncb; ++cb)
-                tma_gather4_2d(dst + cb * (TNS * 128), map, x0 + cb * EPB, y[u][0], y[u][1], y[u][2], y[u][3], bar_full + 8 * s);
-            }
-          }
+          copy_rows<HD * ESZ / 16, TNS>(kdst, kb, kpitch, ycur, lane);
+          copy_rows<HDV * ESZ / 16, TNS>(vdst, vb, vpitch, ycur, lane);
+          cp_async_arrive_noinc(bar_full + 8 * s);
           ++cnt;
         }
         continue;
@@ -281,7 +338,8 @@ fwd_decode_kernel(const DecArgs a, const __grid_constant__ CUtensorMap map_k, co
     if (ok) {   // end-of-stream marker
       const uint32_t s = cnt % NST;
       if (wait_or_abort(bar_empty + 8 * s, ((cnt / NST) & 1) ^ 1, s_abort)) {
-        if (lane == 0) { s_info[4 * s] = -1; mbar_arrive(bar_full + 8 * s); }
+        if (lane == 0) s_info[4 * s] = -1;
+        publish_plain(s);
         ++cnt;
       }
     }
@@ -689,6 +747,8 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
   a.total_work = num_work_slots * kp.hkv * kp.nsplits;
   constexpr int TNS = SM::TNS;
   const bool paged = kp.page_table != nullptr;
+  // (the cp.async producer takes any power-of-two page; measured, pages of 8 and 16 keys are faster as TMA boxes:
+  // 0.49 / 0.70 of the HBM peak against 0.48 / 0.60)
   a.gather = paged && (kp.page_size == 1 || kp.page_size == 2 || kp.page_size == 4);
   // rows per TMA box: a page, a whole stage, or (pages that are an odd multiple of 64 keys under 128-key stages) 64
   a.box_rows = a.gather ? 1 : (!paged ? TNS : (kp.page_size < TNS ? kp.page_size : (kp.page_size % TNS == 0 ? TNS : 64)));
@@ -719,7 +779,7 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
 
 // Shapes the decode route takes: head_dim 64, 128 or 192 (values 128), 16-bit queries, a cache of the same type or
 // (head_dim 128) of e4m3 bytes, K/V contiguous or in pages of 1, 2, 4, 8, 16, 32 or a multiple of 64 keys (the small
-// pages through the gather form of the reference's producers, kernels/fa4_blackwell.cu:8042-8062).  These are the
+// pages row by row, as the reference's cp.async producer does for page size 1, kernels/fa4_blackwell.cu:8936-8947).  These are the
 // head dims of the reference's paged kernel (kernels/fa4_blackwell.cu:9958-9983).
 bool decode_supported(const PlanInput& in) {
   if (in.q_dtype == FA_DT_FP8_E4M3) return false;
@@ -729,7 +789,7 @@ bool decode_supported(const PlanInput& in) {
   if (!hd_ok) return false;
   const int ps = in.page_size;
   // pages of 8, 16 or 32 keys divide a 64-row stage into whole 1024-byte swizzle atoms; multiples of 64 are whole
-  // stages; pages of 1, 2 or 4 keys are gathered four rows at a time
+  // stages; pages of 1, 2 or 4 keys are fetched row by row with cp.async
   if (!(ps == 0 || ps == 1 || ps == 2 || ps == 4 || ps == 8 || ps == 16 || ps == 32 || ps % 64 == 0)) return false;
   return in.hkv > 0 && in.hq % in.hkv == 0 && in.tc_layout_ok;
 }

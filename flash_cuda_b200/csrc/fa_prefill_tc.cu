@@ -46,6 +46,10 @@ constexpr int NTHREADS = 384;   // 12 warps: two softmax warpgroups + one warpgr
 constexpr int WARP_MMA = 8, WARP_TMA = 9;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
+#ifndef FA_CAP_EMU_PAIRS
+#define FA_CAP_EMU_PAIRS 2
+#endif
+constexpr int kCapEmuPairs = FA_CAP_EMU_PAIRS;   // of every four pairs in the fused softcap loop
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
 enum Role : unsigned { ROLE_TMA = 1, ROLE_MMA = 2, ROLE_SOFTMAX = 3, ROLE_EPILOGUE = 4 };
 
@@ -210,7 +214,9 @@ __device__ __noinline__ void load_tile_paged(const TcArgs& a, const CUtensorMap*
 // NTL = query tiles per work item: 2, or 1 where one tile's S (128 columns) and O (HDV > 128 columns) leave no room
 // in the 512 TMEM columns for a second tile (head_dim 256, head_dim 192 with 192 value columns).  With one tile the
 // second softmax warpgroup stays idle and softmax and MMAs of the tile alternate instead of overlapping.
-template <typename T, int HD, int HDV, int KST, int VST, int NTL>
+// CAP: the logit soft cap is compiled in (the host picks the instantiation by softcap > 0, so that the common
+// kernel carries none of its code: the softmax loop's time follows its instruction count).
+template <typename T, int HD, int HDV, int KST, int VST, int NTL, bool CAP>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ CUtensorMap map_q,
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -593,7 +599,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const uint32_t tS = tmem + lane_base + t * TN;
     const uint32_t tO = tmem + lane_base + O_BASE + t * O_STRIDE;
-    const bool has_cap = p.softcap > 0.f;
+    constexpr bool has_cap = CAP;
     uint32_t scnt = 0, ocnt = 0;
     bool ok = true;
 
@@ -657,7 +663,11 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sreg[c]);
         tmem_wait_ld();
         float mx = -INFINITY;
-        if (has_cap) {
+        // tanh is monotonic, so on a block without masked columns the row maximum is taken over the raw scores
+        // and the cap moves into the exponential pass: one stream of tanh / exp2 pairs instead of two passes
+        // over the row with the maximum between them.
+        const bool fuse_cap = !F8 && has_cap && full;
+        if (has_cap && !fuse_cap) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
 #pragma unroll
@@ -687,7 +697,8 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
           mx = fmaxf(fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])),
                      fmaxf(fmaxf(mxa[4], mxa[5]), fmaxf(mxa[6], mxa[7])));
         }
-        const float y_max = mx * c_mul;               // c_mul > 0, so the maximum commutes with the scale
+        // c_mul > 0, so the maximum commutes with the scale
+        const float y_max = (fuse_cap ? tanh_fast(mx * cap_in) : mx) * c_mul;
         float corr = 1.f;
         bool rescale = false;
         // m_used is the reference point of the exponentials, p = 2^(y - m_used).  For 16-bit P it is the row
@@ -722,17 +733,36 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         float2 psum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
         const float2 c2 = make_float2(c_mul, c_mul), nm2 = make_float2(neg_m, neg_m);
         if constexpr (!F8) {
+          if (!fuse_cap) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t pk[16];
+            for (int c = 0; c < 4; ++c) {
+              uint32_t pk[16];
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const float2 y = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
-              const float2 pp = make_float2(ex2(y.x), ex2(y.y));
-              psum[(j >> 1) & 3] = fadd2(psum[(j >> 1) & 3], pp);
-              pk[j >> 1] = pack2<TO>(pp.x, pp.y);
+              for (int j = 0; j < 32; j += 2) {
+                const float2 y = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
+                const float2 pp = make_float2(ex2(y.x), ex2(y.y));
+                psum[(j >> 1) & 3] = fadd2(psum[(j >> 1) & 3], pp);
+                pk[j >> 1] = pack2<TO>(pp.x, pp.y);
+              }
+              tmem_st16(tS + c * 16, pk);
             }
-            tmem_st16(tS + c * 16, pk);
+          } else {
+            const float2 ci2 = make_float2(cap_in, cap_in);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                const float2 x = fmul2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), ci2);
+                const float2 y = ffma2(make_float2(tanh_fast(x.x), tanh_fast(x.y)), c2, nm2);
+                // tanh and exp2 share the special-function unit, which bounds this loop: every fourth pair
+                // takes its exponential on the FMA pipe
+                const float2 pp = (((j >> 1) & 3) < kCapEmuPairs) ? ex2_poly2(y) : make_float2(ex2(y.x), ex2(y.y));
+                psum[(j >> 1) & 3] = fadd2(psum[(j >> 1) & 3], pp);
+                pk[j >> 1] = pack2<TO>(pp.x, pp.y);
+              }
+              tmem_st16(tS + c * 16, pk);
+            }
           }
         } else if (!two_term) {
           // four e4m3 probabilities per TMEM column.  The row sum is taken over the ROUNDED probabilities, so that
@@ -802,6 +832,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         if (lane == 0) mbar_arrive(bar_p_full + 8 * t);
       }
       if (!ok) break;
+      if (CAP && kCapEmuPairs > 0 && m_used == -INFINITY) l = 0.f;   // the cubic never returns exactly 0
 
       // ---- epilogue of this tile ----
       if constexpr (HDV <= 128) {
@@ -1096,8 +1127,8 @@ static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t row
   return true;
 }
 
-template <typename T, int HD, int HDV, int KST, int VST, int NTL = 2>
-static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_rows, cudaStream_t stream) {
+template <typename T, int HD, int HDV, int KST, int VST, int NTL, bool CAP>
+static int launch_cap(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_rows, cudaStream_t stream) {
   using SM = Smem<Elem<T>::kSize, HD, HDV, KST, VST, NTL>;
   TcArgs a;
   a.kp = kp;
@@ -1131,7 +1162,7 @@ static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
                     (uint64_t)kp.o_row_stride, 32))
       a.stage_out = 1;
   }
-  auto kern = fwd_prefill_tc_kernel<T, HD, HDV, KST, VST, NTL>;
+  auto kern = fwd_prefill_tc_kernel<T, HD, HDV, KST, VST, NTL, CAP>;
   int smem = SM::kBytes + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;   // one CTA per SM: the CTA owns all 512 TMEM columns
   static std::atomic<unsigned long long> attr_done{0};   // one bit per device
@@ -1146,6 +1177,12 @@ static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
   if (grid <= 0) return 0;
   kern<<<grid, NTHREADS, smem, stream>>>(a, mq, mk, mv, mo);
   return (int)cudaGetLastError();
+}
+
+template <typename T, int HD, int HDV, int KST, int VST, int NTL = 2>
+static int launch_impl(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_rows, cudaStream_t stream) {
+  return kp.softcap > 0.f ? launch_cap<T, HD, HDV, KST, VST, NTL, true>(kp, pl, dtype, kv_rows, stream)
+                          : launch_cap<T, HD, HDV, KST, VST, NTL, false>(kp, pl, dtype, kv_rows, stream);
 }
 
 }  // namespace tc

@@ -351,6 +351,34 @@ __device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
   return d;
 }
+// 16-byte asynchronous copy global -> shared that bypasses L1; src_bytes = 0 writes zeros instead of reading
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// one arrival on `bar` once every cp.async this thread has issued so far has landed; the barrier's count must
+// include it (the pending count is not raised)
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 2^y for two lanes on the FMA and integer pipes instead of the special-function unit: y = n + f with n the
+// nearest integer (taken from the low mantissa bits of y + 1.5*2^23) and |f| <= 0.5, 2^f by a cubic with a
+// relative error of 7.5e-5, n added into the exponent field.  y is clamped at -126 (the result is then 2^-126,
+// not 0) and must stay below 127.
+__device__ __forceinline__ float2 ex2_poly2(float2 y) {
+  const float kMagic = 12582912.f;
+  y.x = fmaxf(y.x, -126.f);
+  y.y = fmaxf(y.y, -126.f);
+  const float2 r = fadd2(y, make_float2(kMagic, kMagic));
+  const float2 n = fadd2(r, make_float2(-kMagic, -kMagic));
+  const float2 f = fadd2(y, make_float2(-n.x, -n.y));
+  float2 q = ffma2(f, make_float2(0.0551716685f, 0.0551716685f), make_float2(0.242611125f, 0.242611125f));
+  q = ffma2(q, f, make_float2(0.693260968f, 0.693260968f));
+  q = ffma2(q, f, make_float2(0.999928057f, 0.999928057f));
+  float2 o;
+  o.x = __int_as_float(__float_as_int(q.x) + (__float_as_int(r.x) << 23));
+  o.y = __int_as_float(__float_as_int(q.y) + (__float_as_int(r.y) << 23));
+  return o;
+}
 __device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
   unsigned long long ra, rb, rd;
   asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));

@@ -1,4 +1,4 @@
-"""Two real GPUs (skipped when fewer are visible): the sharded drivers give the single-GPU result.
+"""Two, four and eight real GPUs (skipped when fewer are visible): the sharded drivers give the single-GPU result.
 Ranks are child processes over NCCL with NVLS off; a rank only leaves between steps."""
 import os
 import socket
@@ -42,7 +42,7 @@ def _worker(rank, world, port, ret):
             ok_kv = ok_kv and (out.float() - ref_out.float()).abs().max().item() <= 1e-2 and \
                 (lse - ref_lse).abs().max().item() <= 2e-3
         # --- head sharding: each rank its block of kv heads, outputs are the matching slices
-        p = W.make_problem("mg", [(300, 300), (40, 700)], hq=8, hkv=4, hd=128, causal=True, seed=6).to(dev)
+        p = W.make_problem("mg", [(300, 300), (40, 700)], hq=16, hkv=8, hd=128, causal=True, seed=6).to(dev)
         ref2, lse2 = ops.call_fwd(p.q, p.k, p.v, **p.capi_kw())
         o_s, l_s, qs = MG.fwd_head_sharded(p.q, p.k, p.v, rank=rank, world=world, **p.capi_kw())
         ok_h = torch.equal(o_s, ref2[:, qs, :]) and torch.allclose(l_s, lse2[qs], atol=1e-6)
@@ -53,11 +53,12 @@ def _worker(rank, world, port, ret):
         dist.destroy_process_group()
 
 
-def test_two_gpu_sharding_matches_single_gpu():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_sharding_matches_single_gpu(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
-    assert dict(ret) == {0: (True, True), 1: (True, True)}
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert dict(ret) == {r: (True, True) for r in range(world)}
