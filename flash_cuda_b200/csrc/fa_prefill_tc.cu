@@ -65,6 +65,7 @@ struct TcArgs {
   int stage_out;     // map_o is valid: full 32-row groups leave through shared memory and TMA stores
   int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128); 1 in gather mode
   int gather;        // pages of 1, 2 or 4 keys: K/V maps are 2-D with one-row boxes, rows come four per tile::gather4
+  int wide;          // the whole TMA warp produces (lane 0 alone otherwise): see the TMA role
   int kv_total_rows; // rows of the K/V tensor map (out-of-range y => zero fill)
   int out_cols;      // value columns that exist (head_dim 96 runs as 128 with zero-filled columns 96..127)
 };
@@ -170,15 +171,17 @@ struct Ring {
   }
 };
 
-// One K or V tile of a PAGED cache, loaded by the whole producer warp: lane j owns TMA box j of the tile (one page, or
-// 128 keys of a larger page) and looks its page up itself; with pages of 1, 2 or 4 keys lane g owns keys 4g .. 4g+3 and
-// fetches them with one tile::gather4 per 128-byte column block (2-D maps over [rows][heads x head_dim] then).
+// One K or V tile of a PAGED cache.  The TMA boxes of the tile (one page each, or 128 keys of a larger page) are
+// shared out j = j0, j0 + jstride, ..: j0 = lane, jstride = 32 when the whole warp produces (every lane looks the page
+// of its own box up), 0 and 1 when lane 0 produces alone.  With pages of 1, 2 or 4 keys (whole warp only) lane g owns
+// keys 4g .. 4g+3 and fetches them with one tile::gather4 per 128-byte column block (2-D maps over
+// [rows][heads x head_dim] then).
 // Kept out of line and rolled on purpose: the producer shares its instruction cache with the softmax warps, whose
 // loop bodies are large, and the time of this path went with its code size (a fully unrolled single-thread form
 // measured 372 TFLOP/s on pages of 16 keys, the rolled inline form 583).
 template <int EPB>
 __device__ __noinline__ void load_tile_paged(const TcArgs& a, const CUtensorMap* map, int width, uint32_t dst, int nb,
-                                             uint32_t bar, int b, int seqlen_k, int hk, int lane) {
+                                             uint32_t bar, int b, int seqlen_k, int hk, int lane, int j0, int jstride) {
   const KParams& p = a.kp;
   const int32_t* pt = p.page_table + (int64_t)b * p.page_table_stride;
   const int ncb = width / EPB;
@@ -198,8 +201,7 @@ __device__ __noinline__ void load_tile_paged(const TcArgs& a, const CUtensorMap*
       tma_gather4_2d(dst + cb * (TN * 128) + lane * 512, map, hk * width + cb * EPB, y[0], y[1], y[2], y[3], bar);
     return;
   }
-  const int r = lane * a.kv_box_rows;
-  if (r < TN) {
+  for (int r = j0 * a.kv_box_rows; r < TN; r += jstride * a.kv_box_rows) {
     const int kk = nb * TN + r;
     int y = a.kv_total_rows;   // beyond the sequence: out of range => zeros
     if (kk < seqlen_k) {
@@ -292,12 +294,18 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
   asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
   if (warp == WARP_TMA) {
     // =========================================== TMA producer ===========================================
-    // The whole warp runs the control flow; lane 0 (the leader) waits on the barriers, takes work ids, issues the Q
-    // copies and the copies of unpaged K/V tiles; every wait's outcome and every decoded item is broadcast, and for
-    // paged tiles all lanes look pages up and issue copies (load_tile_paged).
-    {
+    // Two forms, chosen by the host (TcArgs::wide).  Wide: the whole warp runs the control flow; lane 0 (the
+    // leader) waits on the barriers, takes work ids, issues the Q copies and the copies of unpaged K/V tiles; every
+    // wait's outcome and every decoded item is broadcast, and for paged tiles all lanes look pages up and issue
+    // copies (load_tile_paged): pages of 16 keys 433 -> 817 TFLOP/s.  Narrow: lane 0 does all of it alone and the
+    // other lanes leave; the broadcasts' latency is then off the path between a freed V stage and its refill, which
+    // is what the kernels with a single V stage (head_dim 192, 256) are bound by: 945 against 868 TFLOP/s wide.
+    // (Compiled twice, the form a template argument: with the choice left to a run-time flag the narrow form kept
+    // the divergence bookkeeping of the wide one and lost 3-12 %.)
+    auto tma_role = [&](auto wide_tag) {
+      constexpr bool wide = decltype(wide_tag)::value;
       constexpr uint32_t FULLM = 0xffffffffu;
-      const bool leader = lane == 0;
+      const bool leader = !wide || lane == 0;
       uint32_t qcnt = 0, k0cnt = 0;
       Ring<KST> kr;
       Ring<VST> vr;
@@ -318,7 +326,8 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
       auto lead_wait = [&](uint32_t bar, uint32_t parity) -> bool {
         int r = 1;
         if (leader) r = wait_or_abort(bar, parity, s_abort) ? 1 : 0;
-        return __shfl_sync(FULLM, r, 0) != 0;
+        if (wide) r = __shfl_sync(FULLM, r, 0);
+        return r != 0;
       };
       // work items are handed out heaviest first: a CTA's first id is its block index, later ones come from one
       // global counter; every role of this CTA learns the item from a two-slot mailbox in shared memory
@@ -347,7 +356,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
           for (int i = 0; i < 4; ++i) dst[i] = src[i];
           mbar_arrive(bar_w_full + 8 * slot);   // release: the slot is visible to whoever observes the phase
         }
-        {
+        if (wide) {
           int* pi = reinterpret_cast<int*>(&it);
 #pragma unroll
           for (int i = 0; i < 16; ++i) pi[i] = __shfl_sync(FULLM, pi[i], 0);
@@ -386,7 +395,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
                 tma_load_3d(dst + cb * (TN * 128), map, cb * EPB, hk, it.k0 + nb * TN, bar);
             }
           } else {
-            load_tile_paged<EPB>(a, map, width, dst, nb, bar, it.b, it.seqlen_k, hk, lane);
+            load_tile_paged<EPB>(a, map, width, dst, nb, bar, it.b, it.seqlen_k, hk, lane, wide ? lane : 0, wide ? 32 : 1);
           }
         };
         // K of the first block has a barrier of its own; every later K tile arrives together with the V tile of
@@ -443,7 +452,9 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         }
         counters_release(p.counters);   // this CTA takes no more tickets
       }
-    }
+    };
+    if (a.wide) tma_role(std::true_type{});
+    else if (lane == 0) tma_role(std::false_type{});
   } else if (warp == WARP_MMA) {
     // =========================================== MMA issuer =============================================
     // The WHOLE warp runs this role's control flow, and every value that steers it (work id, block ranges,
@@ -1139,6 +1150,9 @@ static int launch_cap(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_
   const bool paged = kp.page_table != nullptr;
   a.gather = paged && (kp.page_size == 1 || kp.page_size == 2 || kp.page_size == 4);
   a.kv_box_rows = a.gather ? 1 : (paged ? (kp.page_size < TN ? kp.page_size : TN) : TN);
+  // the whole warp produces where a tile is many boxes and, for paged caches, where K rides on V's barrier (equal
+  // ring depths: measured 1034 -> 1055 TFLOP/s on pages of 64 keys, 1078 -> 1135 on a 1024-row chunk over 32768 keys)
+  a.wide = a.gather || (paged && (kp.page_size <= 32 || KST == VST));
   a.kv_total_rows = (int)kv_rows;
   a.out_cols = kp.hdv;
   CUtensorMap mq, mk, mv, mo;
