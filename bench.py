@@ -628,12 +628,16 @@ def _longctx_leg(args, dist, rank, world, dev, peaks, merge="all_gather"):
         step(i)
     steps = max(1, min(args.steps, 3))
     ms = _time_steps(lambda i: step(i, marks), steps, dist, world)
-    merge_ms = 0.0
+    # Time from the end of a rank's attention kernel to the end of its merge.  On a rank whose kernel ends early
+    # (the last rank is causal on its shard, and GPUs differ by a few per cent) that span also holds the wait for the
+    # slowest kernel; the rank whose kernel ends last waits for nobody, so the MINIMUM over ranks is what the
+    # collective and the merge add to the step.  The maximum is reported beside it.
+    merge_ms = merge_ms_max = 0.0
     if world > 1:
-        merge_ms = sum(marks[2 * i].elapsed_time(marks[2 * i + 1]) for i in range(steps)) / steps
-        t = torch.tensor([merge_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        merge_ms = float(t.item())
+        mine = sum(marks[2 * i].elapsed_time(marks[2 * i + 1]) for i in range(steps)) / steps
+        t = torch.tensor([mine, -mine], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        merge_ms, merge_ms_max = float(t[0].item()), -float(t[1].item())
     val = flops / (ms * 1e-3) / 1e12
     kvgb = (p.k.numel() + p.v.numel()) * 2 / 1e9
     del p
@@ -641,6 +645,7 @@ def _longctx_leg(args, dist, rank, world, dev, peaks, merge="all_gather"):
     return {"metric": "long-context prefill TFLOP/s, whole job (q 4096 x paged KV 524288, 128 heads, hd192/hdv128, causal, bf16)",
             "value": val, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps, "scaling": "strong",
             "gather_and_merge_ms": merge_ms, "gather_and_merge_frac": merge_ms / ms if ms > 0 else None,
+            "gather_and_merge_ms_max_over_ranks": merge_ms_max,
             "parallelism": (f"KV range split over {world} GPU(s) by multi_gpu.fwd_kv_sharded; fp32 partials written into the "
                             f"gather buffer by the kernel, one all-gather (in place), merge kernel reads it in place"
                             if merge == "all_gather" else

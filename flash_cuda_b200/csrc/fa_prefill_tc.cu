@@ -65,7 +65,6 @@ struct TcArgs {
   int stage_out;     // map_o is valid: full 32-row groups leave through shared memory and TMA stores
   int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128); 1 in gather mode
   int gather;        // pages of 1, 2 or 4 keys: K/V maps are 2-D with one-row boxes, rows come four per tile::gather4
-  int wide;          // the whole TMA warp produces (lane 0 alone otherwise): see the TMA role
   int kv_total_rows; // rows of the K/V tensor map (out-of-range y => zero fill)
   int out_cols;      // value columns that exist (head_dim 96 runs as 128 with zero-filled columns 96..127)
 };
@@ -171,43 +170,61 @@ struct Ring {
   }
 };
 
-// One K or V tile of a PAGED cache.  The TMA boxes of the tile (one page each, or 128 keys of a larger page) are
-// shared out j = j0, j0 + jstride, ..: j0 = lane, jstride = 32 when the whole warp produces (every lane looks the page
-// of its own box up), 0 and 1 when lane 0 produces alone.  With pages of 1, 2 or 4 keys (whole warp only) lane g owns
-// keys 4g .. 4g+3 and fetches them with one tile::gather4 per 128-byte column block (2-D maps over
-// [rows][heads x head_dim] then).
-// Kept out of line and rolled on purpose: the producer shares its instruction cache with the softmax warps, whose
-// loop bodies are large, and the time of this path went with its code size (a fully unrolled single-thread form
-// measured 372 TFLOP/s on pages of 16 keys, the rolled inline form 583).
-template <int EPB>
-__device__ __noinline__ void load_tile_paged(const TcArgs& a, const CUtensorMap* map, int width, uint32_t dst, int nb,
-                                             uint32_t bar, int b, int seqlen_k, int hk, int lane, int j0, int jstride) {
+// Paged K/V tiles.  The TMA boxes of a 128-key tile (one page each, or 128 keys of a larger page) are shared out
+// j = j0, j0 + jstride, ..: j0 = lane, jstride = 32 when the whole warp produces (every lane owns one box), 0 and 1
+// when lane 0 produces alone (pages of >= 64 keys then: at most two boxes).  With pages of 1, 2 or 4 keys (whole
+// warp only) lane g owns keys 4g .. 4g+3 and fetches them with one tile::gather4 per 128-byte column block (2-D
+// maps over [rows][heads x head_dim] then).  Either way a lane's share of a tile is at most four pool rows.
+struct PageRows { int y[4]; };
+
+// The pool rows of key block nb.  K and V share the page table, so one look-up serves K(nb) and V(nb); it is made a
+// block ahead and BEFORE the waits for the free stages, so that the page-table loads fly during the waits (the
+// refill of a single V stage is on the critical path: with the look-up after the wait the long-context shape ran
+// at 0.73 of its speed over contiguous keys).  Inlined so that the loads' results are awaited at their first use.
+__device__ __forceinline__ PageRows page_rows(const TcArgs& a, int nb, int b, int seqlen_k, int lane, int j0, int jstride) {
   const KParams& p = a.kp;
   const int32_t* pt = p.page_table + (int64_t)b * p.page_table_stride;
-  const int ncb = width / EPB;
+  PageRows pr;
   if (a.gather) {
-    int y[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int kk = nb * TN + 4 * lane + j;
-      y[j] = 0;                  // beyond the sequence: pool row 0 (finite by contract), masked by the softmax
+      pr.y[j] = 0;               // beyond the sequence: pool row 0 (finite by contract), masked by the softmax
       if (kk < seqlen_k) {
         const int lp = kk >> p.page_shift;
-        y[j] = (pt[lp] << p.page_shift) + (kk - (lp << p.page_shift));
+        pr.y[j] = (pt[lp] << p.page_shift) + (kk - (lp << p.page_shift));
       }
     }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = (j0 + i * jstride) * a.kv_box_rows, kk = nb * TN + r;
+      pr.y[i] = a.kv_total_rows;   // beyond the sequence: out of range => zeros
+      if (r < TN && kk < seqlen_k) {
+        const int lp = p.page_shift >= 0 ? (kk >> p.page_shift) : (kk / p.page_size);
+        pr.y[i] = pt[lp] * p.page_size + (kk - lp * p.page_size);
+      }
+    }
+  }
+  return pr;
+}
+
+// The copies of one paged K or V tile.  Rolled on purpose: the producer shares its instruction cache with the
+// softmax warps, whose loop bodies are large, and the time of this path went with its code size (a fully unrolled
+// single-thread form measured 372 TFLOP/s on pages of 16 keys, a rolled one 583).
+template <int EPB>
+__device__ __forceinline__ void load_tile_paged(const TcArgs& a, const CUtensorMap* map, int width, uint32_t dst, uint32_t bar,
+                                             int hk, int r0, int rstride, int y0, int y1, int y2, int y3) {
+  const int ncb = width / EPB;
+  if (a.gather) {
 #pragma unroll 1
     for (int cb = 0; cb < ncb; ++cb)
-      tma_gather4_2d(dst + cb * (TN * 128) + lane * 512, map, hk * width + cb * EPB, y[0], y[1], y[2], y[3], bar);
+      tma_gather4_2d(dst + cb * (TN * 128) + r0 * 128, map, hk * width + cb * EPB, y0, y1, y2, y3, bar);
     return;
   }
-  for (int r = j0 * a.kv_box_rows; r < TN; r += jstride * a.kv_box_rows) {
-    const int kk = nb * TN + r;
-    int y = a.kv_total_rows;   // beyond the sequence: out of range => zeros
-    if (kk < seqlen_k) {
-      const int lp = p.page_shift >= 0 ? (kk >> p.page_shift) : (kk / p.page_size);
-      y = pt[lp] * p.page_size + (kk - lp * p.page_size);
-    }
+#pragma unroll 1
+  for (int i = 0, r = r0; i < 4 && r < TN; ++i, r += rstride) {
+    const int y = i == 0 ? y0 : (i == 1 ? y1 : (i == 2 ? y2 : y3));
 #pragma unroll 1
     for (int cb = 0; cb < ncb; ++cb) tma_load_3d(dst + cb * (TN * 128) + r * 128, map, cb * EPB, hk, y, bar);
   }
@@ -218,7 +235,10 @@ __device__ __noinline__ void load_tile_paged(const TcArgs& a, const CUtensorMap*
 // second softmax warpgroup stays idle and softmax and MMAs of the tile alternate instead of overlapping.
 // CAP: the logit soft cap is compiled in (the host picks the instantiation by softcap > 0, so that the common
 // kernel carries none of its code: the softmax loop's time follows its instruction count).
-template <typename T, int HD, int HDV, int KST, int VST, int NTL, bool CAP>
+// PROD: the form of the TMA producer: 0 = contiguous K/V, lane 0 alone; 1 = paged, lane 0 alone; 2 = paged, the whole
+// warp (see the TMA role).  Template arguments rather than run-time flags for the same reason as CAP: code that a
+// launch never runs still moved the time of the code it does run by a few per cent.
+template <typename T, int HD, int HDV, int KST, int VST, int NTL, bool CAP, int PROD>
 __global__ void __launch_bounds__(NTHREADS, 1)
 fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ CUtensorMap map_q,
                       const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -294,16 +314,17 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
   asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
   if (warp == WARP_TMA) {
     // =========================================== TMA producer ===========================================
-    // Two forms, chosen by the host (TcArgs::wide).  Wide: the whole warp runs the control flow; lane 0 (the
+    // Two forms, chosen by the host (template argument PROD).  Wide: the whole warp runs the control flow; lane 0 (the
     // leader) waits on the barriers, takes work ids, issues the Q copies and the copies of unpaged K/V tiles; every
     // wait's outcome and every decoded item is broadcast, and for paged tiles all lanes look pages up and issue
     // copies (load_tile_paged): pages of 16 keys 433 -> 817 TFLOP/s.  Narrow: lane 0 does all of it alone and the
     // other lanes leave; the broadcasts' latency is then off the path between a freed V stage and its refill, which
     // is what the kernels with a single V stage (head_dim 192, 256) are bound by: 945 against 868 TFLOP/s wide.
-    // (Compiled twice, the form a template argument: with the choice left to a run-time flag the narrow form kept
-    // the divergence bookkeeping of the wide one and lost 3-12 %.)
-    auto tma_role = [&](auto wide_tag) {
-      constexpr bool wide = decltype(wide_tag)::value;
+    // (The form is a template argument: with the choice left to a run-time flag the narrow form kept the
+    // divergence bookkeeping of the wide one and lost 3-12 %.)
+    constexpr bool wide = PROD == 2;
+    constexpr bool paged = PROD != 0;
+    if (wide || lane == 0) {
       constexpr uint32_t FULLM = 0xffffffffu;
       const bool leader = !wide || lane == 0;
       uint32_t qcnt = 0, k0cnt = 0;
@@ -388,25 +409,30 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
         const int hk = it.h / p.rep;
         // one K or V tile of key block nb into `dst`, completing on `bar`
-        auto load_tile = [&](const CUtensorMap* map, int width, uint32_t dst, int nb, uint32_t bar) {
-          if (p.page_table == nullptr) {
+        const int pj0 = wide ? lane : 0, pjs = wide ? 32 : 1;
+        // first row of this lane's first box and the distance to its next one (gather: four rows per lane)
+        const int pr0 = a.gather ? 4 * lane : pj0 * a.kv_box_rows, prs = pjs * a.kv_box_rows;
+        auto load_tile = [&](const CUtensorMap* map, int width, uint32_t dst, int nb, uint32_t bar, const PageRows& pr) {
+          if (!paged) {
             if (leader) {
               for (int cb = 0; cb < width / EPB; ++cb)
                 tma_load_3d(dst + cb * (TN * 128), map, cb * EPB, hk, it.k0 + nb * TN, bar);
             }
           } else {
-            load_tile_paged<EPB>(a, map, width, dst, nb, bar, it.b, it.seqlen_k, hk, lane, wide ? lane : 0, wide ? 32 : 1);
+            load_tile_paged<EPB>(a, map, width, dst, bar, hk, pr0, prs, pr.y[0], pr.y[1], pr.y[2], pr.y[3]);
           }
         };
         // K of the first block has a barrier of its own; every later K tile arrives together with the V tile of
         // the block before it (the MMA warp needs both at the same point), so the consumer waits once per block
+        PageRows rows_cur = {{0, 0, 0, 0}};
+        if (paged) rows_cur = page_rows(a, it.ulo, it.b, it.seqlen_k, lane, pj0, pjs);
         {
           const uint32_t s = kr.slot;
           ok = lead_wait(bar_k_empty + 8 * s, kr.phase ^ 1u);
           if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
           const uint32_t kbar = MERGE_KV ? bar_k0_full : bar_k_full + 8 * s;
           if (leader) mbar_expect_tx(kbar, SM::kKStage);
-          load_tile(&map_k, HD, sK + s * SM::kKStage, it.ulo, kbar);
+          load_tile(&map_k, HD, sK + s * SM::kKStage, it.ulo, kbar, rows_cur);
           kr.advance();
           ++k0cnt;
         }
@@ -418,18 +444,21 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         for (int nb = it.ulo; nb < it.uhi; ++nb) {
           const bool nxt = nb + 1 < it.uhi;
           const uint32_t vs = vr.slot, ks = kr.slot;
+          PageRows rows_nxt = rows_cur;
+          if (paged && nxt) rows_nxt = page_rows(a, nb + 1, it.b, it.seqlen_k, lane, pj0, pjs);
           ok = lead_wait(bar_v_empty + 8 * vs, vr.phase ^ 1u);
           if (ok && nxt) ok = lead_wait(bar_k_empty + 8 * ks, kr.phase ^ 1u);
           if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
           if (leader) mbar_expect_tx(bar_v_full + 8 * vs, SM::kVStage + ((MERGE_KV && nxt) ? SM::kKStage : 0));
-          load_tile(&map_v, HDV, sV + vs * SM::kVStage, nb, bar_v_full + 8 * vs);
+          load_tile(&map_v, HDV, sV + vs * SM::kVStage, nb, bar_v_full + 8 * vs, rows_cur);
           vr.advance();
           if (nxt) {
             const uint32_t kbar = MERGE_KV ? bar_v_full + 8 * vs : bar_k_full + 8 * ks;
             if constexpr (!MERGE_KV) { if (leader) mbar_expect_tx(kbar, SM::kKStage); }
-            load_tile(&map_k, HD, sK + ks * SM::kKStage, nb + 1, kbar);
+            load_tile(&map_k, HD, sK + ks * SM::kKStage, nb + 1, kbar, rows_nxt);
             kr.advance();
           }
+          rows_cur = rows_nxt;
           if (nb == it.ulo) it_next = fetch_and_publish();
         }
       }
@@ -452,9 +481,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         }
         counters_release(p.counters);   // this CTA takes no more tickets
       }
-    };
-    if (a.wide) tma_role(std::true_type{});
-    else if (lane == 0) tma_role(std::false_type{});
+    }
   } else if (warp == WARP_MMA) {
     // =========================================== MMA issuer =============================================
     // The WHOLE warp runs this role's control flow, and every value that steers it (work id, block ranges,
@@ -602,8 +629,13 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
     if (leader) umma_commit(bar_drain);
     wait_or_abort(bar_drain, 0, s_abort + 1);
   }
+  } else if (NTL == 1 && warp >= 4) {
+    // one tile per item: warps 4-7 have no rows; they hand their registers to warps 0-3, whose epilogue holds a
+    // 256-column O row, and wait at the final barrier
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
   } else {
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+    if constexpr (NTL == 1) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    else asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
     // ========================================= softmax + epilogue =======================================
     const int t = warp >> 2;                       // tile of this warpgroup
     const int r = (warp & 3) * 32 + lane;          // row within the tile == TMEM lane
@@ -629,10 +661,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
       ++wcnt;
       return it;
     };
-    // (with one tile per item the second softmax warpgroup has no rows: it takes no part in the hand-offs)
-    const bool has_tile = NTL == 2 || t == 0;
-    for (Item it = (has_tile ? next_work() : Item{0, 0, 0, 0, 0, 0, 0, 0, {0, 0}, {0, 0}, 0, 0, 0, kEndOfWork});
-         it.w != kEndOfWork && ok; it = next_work()) {
+    for (Item it = next_work(); it.w != kEndOfWork && ok; it = next_work()) {
       if (!it.valid) continue;
       const int row0 = it.pair * (NTL * TM) + t * TM;
       if (row0 >= it.seqlen_q) continue;           // this tile owns no row
@@ -1138,8 +1167,17 @@ static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t row
   return true;
 }
 
-template <typename T, int HD, int HDV, int KST, int VST, int NTL, bool CAP>
-static int launch_cap(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_rows, cudaStream_t stream) {
+// The whole warp produces where a tile is many boxes (pages of <= 32 keys, gathered rows) and, on pages of 64 keys,
+// where K rides on V's barrier (equal ring depths: measured 1034 -> 1055 TFLOP/s, 1078 -> 1135 on a 1024-row chunk
+// over 32768 keys); lane 0 alone otherwise (a tile of a page of >= 128 keys is one box: 1143 against 1117 wide).
+template <int KST, int VST>
+static bool producer_is_wide(const KParams& kp) {
+  if (kp.page_table == nullptr) return false;
+  return kp.page_size <= 32 || (KST == VST && kp.page_size <= 64);
+}
+
+template <typename T, int HD, int HDV, int KST, int VST, int NTL, bool CAP, int PROD>
+static int launch_prod(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_rows, cudaStream_t stream) {
   using SM = Smem<Elem<T>::kSize, HD, HDV, KST, VST, NTL>;
   TcArgs a;
   a.kp = kp;
@@ -1150,9 +1188,7 @@ static int launch_cap(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_
   const bool paged = kp.page_table != nullptr;
   a.gather = paged && (kp.page_size == 1 || kp.page_size == 2 || kp.page_size == 4);
   a.kv_box_rows = a.gather ? 1 : (paged ? (kp.page_size < TN ? kp.page_size : TN) : TN);
-  // the whole warp produces where a tile is many boxes and, for paged caches, where K rides on V's barrier (equal
-  // ring depths: measured 1034 -> 1055 TFLOP/s on pages of 64 keys, 1078 -> 1135 on a 1024-row chunk over 32768 keys)
-  a.wide = a.gather || (paged && (kp.page_size <= 32 || KST == VST));
+  if ((PROD != 0) != paged || (PROD == 2) != producer_is_wide<KST, VST>(kp)) return -1;
   a.kv_total_rows = (int)kv_rows;
   a.out_cols = kp.hdv;
   CUtensorMap mq, mk, mv, mo;
@@ -1176,7 +1212,7 @@ static int launch_cap(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_
                     (uint64_t)kp.o_row_stride, 32))
       a.stage_out = 1;
   }
-  auto kern = fwd_prefill_tc_kernel<T, HD, HDV, KST, VST, NTL, CAP>;
+  auto kern = fwd_prefill_tc_kernel<T, HD, HDV, KST, VST, NTL, CAP, PROD>;
   int smem = SM::kBytes + 1024;
   if (smem < 120 * 1024) smem = 120 * 1024;   // one CTA per SM: the CTA owns all 512 TMEM columns
   static std::atomic<unsigned long long> attr_done{0};   // one bit per device
@@ -1191,6 +1227,13 @@ static int launch_cap(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_
   if (grid <= 0) return 0;
   kern<<<grid, NTHREADS, smem, stream>>>(a, mq, mk, mv, mo);
   return (int)cudaGetLastError();
+}
+
+template <typename T, int HD, int HDV, int KST, int VST, int NTL, bool CAP>
+static int launch_cap(const KParams& kp, const Plan& pl, int dtype, uint64_t kv_rows, cudaStream_t stream) {
+  if (kp.page_table == nullptr) return launch_prod<T, HD, HDV, KST, VST, NTL, CAP, 0>(kp, pl, dtype, kv_rows, stream);
+  return producer_is_wide<KST, VST>(kp) ? launch_prod<T, HD, HDV, KST, VST, NTL, CAP, 2>(kp, pl, dtype, kv_rows, stream)
+                                        : launch_prod<T, HD, HDV, KST, VST, NTL, CAP, 1>(kp, pl, dtype, kv_rows, stream);
 }
 
 template <typename T, int HD, int HDV, int KST, int VST, int NTL = 2>
