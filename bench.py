@@ -606,13 +606,14 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
-def _longctx_leg(args, dist, rank, world, dev, peaks, merge="all_gather"):
+def _longctx_leg(args, dist, rank, world, dev, peaks, merge="auto"):
     """B=1, a chunk of 4096 query rows against a paged KV of 524288 tokens (page 64), 128 heads, head_dim 192 /
     head_dim_v 128, causal, bf16.  The key range is split evenly over the ranks (strong scaling); each rank's kernel
     writes its fp32 partial into the gather buffer, ONE all-gather + the merge kernel finish the step, all inside
     the timed region; the time between the end of the attention kernel and the end of the merge is reported apart."""
     from flash_cuda_b200 import multi_gpu as MG, workloads as W
     q_len, k_len, heads = 4096, args.longctx_keys, 128
+    merge = MG.resolve_merge(merge, world, q_len)
     per = k_len // world
     p = W.long_context(dev, seed=0, q_len=q_len, k_len=k_len, heads=heads, k_begin=rank * per, k_end=(rank + 1) * per)
     pairs = q_len * (k_len - q_len) + q_len * (q_len + 1) // 2     # unmasked pairs per head of the WHOLE problem
@@ -651,7 +652,10 @@ def _longctx_leg(args, dist, rank, world, dev, peaks, merge="all_gather"):
                             if merge == "all_gather" else
                             f"KV range split over {world} GPU(s); partial rows exchanged by all-to-all, merged per row block, result all-gathered"),
             "roofline": _tensor_roofline(val / world, peaks, sustained=True),
-            "kernels_per_step": ["fwd_prefill_tc_kernel"] + ([] if world == 1 else ["ncclAllGather (NCCL)", "combine_kernel"]),
+            "merge": merge if world > 1 else None,
+            "kernels_per_step": ["fwd_prefill_tc_kernel"] + ([] if world == 1 else
+                                 ["ncclAllGather (NCCL)", "combine_kernel"] if merge == "all_gather" else
+                                 ["ncclSendRecv x2 (NCCL all-to-all)", "combine_kernel", "ncclAllGather x2 (NCCL)"]),
             "l2": f"KV shard {kvgb:.1f} GB per GPU (> L2)"}
 
 
@@ -701,7 +705,7 @@ def main():
     ap.add_argument("--decode-ctx-max", type=int, default=32768, help="--decode-only: longest context (captures use a smaller pool)")
     ap.add_argument("--decode-batch", type=int, default=128, help="decode batch (128 = the benchmark configuration; "
                     "smaller values are for profiler captures only)")
-    ap.add_argument("--longctx-merge", default="all_gather", choices=["all_gather", "all_to_all"])
+    ap.add_argument("--longctx-merge", default="auto", choices=["auto", "all_gather", "all_to_all"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--batch", type=int, default=4, help="prefill batch per GPU (4 = the benchmark configuration; "
