@@ -54,6 +54,10 @@ constexpr float kRescaleThreshold = 8.0f;   // log2 units
 enum Role : unsigned { ROLE_TMA = 1, ROLE_MMA = 2, ROLE_SOFTMAX = 3, ROLE_EPILOGUE = 4 };
 
 constexpr int kEndOfWork = 0x7fffffff;
+#ifndef FA_HEAD_MAJOR_MB
+#define FA_HEAD_MAJOR_MB 96.0
+#endif
+constexpr double kHeadMajorBytes = FA_HEAD_MAJOR_MB * 1024 * 1024;   // K/V footprint above which work ids are ordered by kv head
 constexpr int kTwoTermBlocks = 2;   // e4m3: tiles that see at most this many key blocks keep P as two e4m3 terms
 
 struct TcArgs {
@@ -62,6 +66,7 @@ struct TcArgs {
   int max_pairs;     // work items per (batch, head): ceil(max_seqlen_q / rows per item)
   int item_rows;     // query rows per work item: 256 (two tiles) or 128 (one tile: head dims whose O needs > 128 columns)
   int use_list;      // kp.work holds scheduler metadata of this route: items = its valid entries x hq
+  int head_major;    // arithmetic order: all tiles of one (batch, kv head) are consecutive ids (K/V larger than L2)
   int stage_out;     // map_o is valid: full 32-row groups leave through shared memory and TMA stores
   int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128); 1 in gather mode
   int gather;        // pages of 1, 2 or 4 keys: K/V maps are 2-D with one-row boxes, rows come four per tile::gather4
@@ -130,6 +135,16 @@ __device__ __forceinline__ Item decode_item(const TcArgs& a, int w, bool* bad_en
       it.lo[0] = it.lo[1] = it.hi[0] = it.hi[1] = it.ulo = it.uhi = it.valid = 0;
       return it;
     }
+  } else if (a.head_major) {
+    // K/V that does not fit in L2: the tiles of one (batch, kv head) run at the same time on neighbouring CTAs and
+    // walk its keys together, so each key block comes from HBM once instead of once per tile (heavy tiles first
+    // within the head)
+    const int per_head = a.max_pairs * p.rep;
+    const int g = w / per_head, rem = w - g * per_head;
+    const int slot = rem / p.rep;
+    it.b = g / p.hkv;
+    it.h = (g - it.b * p.hkv) * p.rep + (rem - slot * p.rep);
+    it.pair = a.max_pairs - 1 - slot;
   } else {
     const int per_slot = p.batch * p.hq;
     const int slot = w / per_slot, rem = w - slot * per_slot;
@@ -1185,6 +1200,11 @@ static int launch_prod(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
   a.max_pairs = (kp.max_seqlen_q + a.item_rows - 1) / a.item_rows;
   a.num_items = kp.batch * kp.hq * a.max_pairs;
   a.use_list = kp.work != nullptr;
+  // bytes of K and V the batch can touch, against the L2 capacity the tiles of concurrently running heads share
+  {
+    const double kv_bytes = (double)kp.batch * kp.hkv * (double)kp.max_seqlen_k * (kp.hd + kp.hdv) * Elem<T>::kSize;
+    a.head_major = kv_bytes > kHeadMajorBytes;
+  }
   const bool paged = kp.page_table != nullptr;
   a.gather = paged && (kp.page_size == 1 || kp.page_size == 2 || kp.page_size == 4);
   a.kv_box_rows = a.gather ? 1 : (paged ? (kp.page_size < TN ? kp.page_size : TN) : TN);
