@@ -123,9 +123,18 @@ __device__ __forceinline__ Item decode_item(const TcArgs& a, int w, bool* bad_en
   Item it;
   it.w = w;
   if (a.use_list) {
-    // entry e of the sorted list = (batch, tile of item_rows rows); all q heads of one entry are consecutive work ids
-    const int e = w / p.hq;
-    it.h = w - e * p.hq;
+    // entry e of the sorted list = (batch, tile of item_rows rows); all q heads of one entry are consecutive work
+    // ids, or (K/V larger than L2) the kv head is the slowest index and the list is walked once per kv head
+    int e;
+    if (a.head_major) {
+      const int per_kv = p.work[6] * p.rep;
+      const int hk = w / per_kv, rem = w - hk * per_kv;
+      e = rem / p.rep;
+      it.h = hk * p.rep + (rem - e * p.rep);
+    } else {
+      e = w / p.hq;
+      it.h = w - e * p.hq;
+    }
     const int32_t* ent = p.work + kSchedHeader + 4 * e;
     it.b = ent[0];
     it.pair = ent[1];

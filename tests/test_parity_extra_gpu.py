@@ -213,6 +213,25 @@ def test_prefill_route_consumes_scheduler_metadata(cuda_device):
     _check(p, cuda_device, AUTO, 2e-2, scheduler_metadata=md)
 
 
+def test_work_order_by_kv_head(cuda_device):
+    """A K/V footprint above the L2 size switches the prefill kernel's work order to kv-head-major (arithmetic
+    order and metadata list alike).  The footprint is judged from max_seqlen_k, which may be an upper bound: a large
+    bound selects that order on a small problem.  The order changes which CTA computes what, not the result."""
+    p = W.make_problem("kvmajor", [(700, 700), (30, 30), (257, 900), (1300, 1300)], hq=8, hkv=2, hd=128,
+                       causal=True, seed=55)
+    ref_out, ref_lse = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
+    pd = p.to(cuda_device)
+    base, base_lse, _ = capi.fwd(pd.q, pd.k, pd.v, route=TC, check=True, **pd.capi_kw())
+    kw = dict(pd.capi_kw(), max_seqlen_k=1 << 22)
+    md = _metadata_for(p, cuda_device, max_seqlen_k=kw["max_seqlen_k"])
+    assert int(md[9]) == TC
+    for extra in ({}, {"scheduler_metadata": md}):
+        out, lse, _ = capi.fwd(pd.q, pd.k, pd.v, route=TC, check=True, **kw, **extra)
+        assert torch.equal(out, base) and torch.equal(lse, base_lse)
+    assert (base.float().cpu() - ref_out).abs().max().item() <= 2e-2
+    assert (base_lse.cpu() - ref_lse).abs().max().item() <= 2e-3
+
+
 @pytest.mark.parametrize("kind", ["decode", "prefill"])
 def test_metadata_of_another_problem_is_refused(kind, cuda_device):
     """Metadata built for batch 5 handed to a batch-3 call.  It is long enough that no read could leave the
