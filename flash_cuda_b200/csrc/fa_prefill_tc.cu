@@ -51,13 +51,17 @@ constexpr float kLn2 = 0.6931471805599453f;
 #endif
 constexpr int kCapEmuPairs = FA_CAP_EMU_PAIRS;   // of every four pairs in the fused softcap loop
 constexpr float kRescaleThreshold = 8.0f;   // log2 units
+constexpr float kFastSumLimit = 16384.f;    // 2^14: row sum of a block above which the fast softmax form is redone
 enum Role : unsigned { ROLE_TMA = 1, ROLE_MMA = 2, ROLE_SOFTMAX = 3, ROLE_EPILOGUE = 4 };
 
 constexpr int kEndOfWork = 0x7fffffff;
+// K/V footprint above which work ids are ordered by kv head: 1.5 x the L2 capacity.  (Below it the order costs:
+// the tiles of a head then ask the same L2 lines at the same time; 2 x 16 heads x 4096 keys of head_dim 256, 134 MB,
+// ran at 735 TFLOP/s kv-head-major against 827.)
 #ifndef FA_HEAD_MAJOR_MB
-#define FA_HEAD_MAJOR_MB 96.0
+#define FA_HEAD_MAJOR_MB 192.0
 #endif
-constexpr double kHeadMajorBytes = FA_HEAD_MAJOR_MB * 1024 * 1024;   // K/V footprint above which work ids are ordered by kv head
+constexpr double kHeadMajorBytes = FA_HEAD_MAJOR_MB * 1024 * 1024;
 constexpr int kTwoTermBlocks = 2;   // e4m3: tiles that see at most this many key blocks keep P as two e4m3 terms
 
 struct TcArgs {
@@ -726,6 +730,41 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
 #pragma unroll
         for (int c = 0; c < 4; ++c) tmem_ld32(tS + c * 32, sreg[c]);
         tmem_wait_ld();
+        // Fast form of a block (16-bit P, no cap, no masked column, a reference point already taken): the
+        // exponentials are taken against the reference point as it stands, WITHOUT looking for the row maximum
+        // first (64 of the ~400 instructions of a block, and the chain's time follows its instruction count).
+        // Whether the reference was too low shows in the block's row sum afterwards: a probability above
+        // 2^kFastShift makes the sum exceed it.  Then (rare: the maximum must have grown by more than kFastShift
+        // in log2 units since the reference was taken) the block is done again in the general form below, which
+        // overwrites P; nothing has been handed to the MMA warp yet.  Both forms leave P within 2^14, far inside
+        // the range of bf16 and fp16, and its relative precision does not depend on the magnitude.
+        bool fast_done = false;
+        if constexpr (!F8 && !CAP) {
+          if (__all_sync(0xffffffffu, full && m_used != -INFINITY)) {
+            float2 fs[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+            const float2 c2 = make_float2(c_mul, c_mul), nm2 = make_float2(-m_used, -m_used);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t pk[16];
+#pragma unroll
+              for (int j = 0; j < 32; j += 2) {
+                const float2 y = ffma2(make_float2(__uint_as_float(sreg[c][j]), __uint_as_float(sreg[c][j + 1])), c2, nm2);
+                const float2 pp = make_float2(ex2(y.x), ex2(y.y));
+                fs[(j >> 1) & 3] = fadd2(fs[(j >> 1) & 3], pp);
+                pk[j >> 1] = pack2<TO>(pp.x, pp.y);
+              }
+              tmem_st16(tS + c * 16, pk);
+            }
+            const float2 s01 = fadd2(fs[0], fs[1]), s23 = fadd2(fs[2], fs[3]);
+            const float2 s4 = fadd2(s01, s23);
+            const float blk = s4.x + s4.y;
+            if (!__any_sync(0xffffffffu, !(blk <= kFastSumLimit))) {   // (a NaN sum takes the general form too)
+              l += blk;
+              fast_done = true;
+            }
+          }
+        }
+        if (!fast_done) {
         float mx = -INFINITY;
         // tanh is monotonic, so on a block without masked columns the row maximum is taken over the raw scores
         // and the cap moves into the exponential pass: one stream of tanh / exp2 pairs instead of two passes
@@ -890,6 +929,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
           const float2 s4 = fadd2(s01, s23);
           l += s4.x + s4.y;
         }
+        }   // general form
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
