@@ -213,6 +213,24 @@ def test_prefill_route_consumes_scheduler_metadata(cuda_device):
     _check(p, cuda_device, AUTO, 2e-2, scheduler_metadata=md)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp16"])
+@pytest.mark.parametrize("growth", [3.0, 12.0])
+def test_row_maximum_that_grows_late(growth, dtype, cuda_device):
+    """Keys whose scores grow along the sequence: every 128-key block raises the row maxima, by a few log2 units
+    (the lazy reference point stays) or by tens (the block's row sum exposes the stale reference point and the
+    block is redone with a new one).  Non-causal, so that every block takes the prefill kernel's fast form."""
+    p = W.make_problem("late_max", [(300, 1024), (128, 640)], hq=4, hkv=2, hd=128, causal=False, dtype=dtype, seed=56)
+    # block j of the keys is scaled so that its largest logits sit about j * growth (natural-log units) higher
+    q_rms = p.q.float().pow(2).mean().sqrt().item()
+    for (k0, k1) in zip(p.cu_seqlens_k[:-1].tolist(), p.cu_seqlens_k[1:].tolist()):
+        for j, b0 in enumerate(range(k0, k1, 128)):
+            blk = p.k[b0:min(b0 + 128, k1)].float()
+            bump = j * growth / (p.softmax_scale * q_rms * 128 ** 0.5 * 3.0)
+            p.k[b0:min(b0 + 128, k1)] = (blk * (1.0 + bump)).to(p.k.dtype)
+    for route in (TC, AUTO):
+        _check(p, cuda_device, route, 3e-2)
+
+
 def test_work_order_by_kv_head(cuda_device):
     """A K/V footprint above the L2 size switches the prefill kernel's work order to kv-head-major (arithmetic
     order and metadata list alike).  The footprint is judged from max_seqlen_k, which may be an upper bound: a large
