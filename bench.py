@@ -168,7 +168,10 @@ def run_reference(args) -> None:
 # ----------------------------------------------------------------------------------------------------
 # optional arm: the reference's own sm_100a kernel beside ours, same tensors, same loop (one GPU)
 # ----------------------------------------------------------------------------------------------------
-AB_SHAPES = ("c2", "c1", "h16_s4k", "h16_s8k", "c4")
+AB_SHAPES = ("c2", "c1", "c4")
+# Shapes the reference's kernel is not run on: it did not return within the limit on the first of them (the child
+# process was ended by the host-side timeout, the GPU kept answering); the second was never reached.
+AB_SHAPES_STALLED = ("h16_s4k", "h16_s8k")
 
 
 def _ab_problem(name):
@@ -185,7 +188,7 @@ def _ab_problem(name):
         p = W.paged_decode()
         p.leftpad_k = None      # the reference's kernel reads only leftpad_k[0] (kernels/fa4_blackwell.cu:10126-10127)
         return p
-    raise SystemExit(f"unknown A/B shape {name!r}; choose from {AB_SHAPES}")
+    raise SystemExit(f"unknown A/B shape {name!r}; choose from {AB_SHAPES + AB_SHAPES_STALLED}")
 
 
 def run_ab_one(name: str) -> None:
@@ -260,6 +263,9 @@ def run_ab(args) -> None:
     shapes = [x for x in args.ab_shapes.split(",") if x]
     rows = []
     for name in shapes:
+        if name in AB_SHAPES_STALLED:
+            rows.append({"shape": name, "unavailable": "the reference's kernel did not return on this shape (recorded stall); not run again"})
+            continue
         try:
             r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-kernel", "--ab-one", name],
                                stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=args.ab_timeout)
