@@ -97,8 +97,8 @@ def test_small_pages(page_size, cuda_device):
 @pytest.mark.parametrize("kv_dtype", [None, "fp8"])
 @pytest.mark.parametrize("page_size", [1, 2, 4, 8])
 def test_decode_route_gathers_small_pages(page_size, kv_dtype, cuda_device):
-    """The streaming decode kernel over pages of 1, 2 and 4 keys (rows gathered four at a time) and of 8 keys, with a
-    permuted page table, leftpad, ragged ends, several query tokens and split-KV."""
+    """The streaming decode kernel over pages of 1, 2 and 4 keys (rows fetched 16 bytes per lane with cp.async) and
+    of 8 keys (TMA boxes), with a permuted page table, leftpad, ragged ends, several query tokens and split-KV."""
     p = W.make_problem(f"dec_gather_p{page_size}_{kv_dtype}", [(1, 1000), (2, 257), (1, 64), (1, 3), (4, 130)], hq=8,
                        hkv=2, hd=128, causal=True, page_size=page_size, leftpad=[9, 0, 0, 1, 66], kv_dtype=kv_dtype,
                        sink=True, seed=55)
@@ -106,6 +106,17 @@ def test_decode_route_gathers_small_pages(page_size, kv_dtype, cuda_device):
     _check(p, cuda_device, DEC, tol)
     _check(p, cuda_device, DEC, tol, num_splits=3)
     _check(p, cuda_device, AUTO, tol)
+
+
+@pytest.mark.parametrize("hd,hdv", [(64, 64), (192, 128)])
+@pytest.mark.parametrize("page_size", [1, 4])
+def test_decode_route_small_pages_other_head_dims(page_size, hd, hdv, cuda_device):
+    """The cp.async producer's other row widths: 128-byte rows (head_dim 64: four rows per instruction) and 384-byte
+    rows (head_dim 192: a row's chunks straddle instructions)."""
+    p = W.make_problem(f"dec_small_hd{hd}_p{page_size}", [(1, 700), (2, 257), (1, 65), (1, 2)], hq=8, hkv=2, hd=hd,
+                       hdv=hdv, causal=True, page_size=page_size, leftpad=[5, 0, 0, 0], seed=57)
+    _check(p, cuda_device, DEC, 2e-2)
+    _check(p, cuda_device, DEC, 2e-2, num_splits=2)
 
 
 @pytest.mark.parametrize("page_size", [1, 2, 4, 8, 16, 32, 64, 128, 256])
