@@ -750,8 +750,10 @@ static int launch_t(const KParams& kp, const Plan& pl, int num_work_slots, cudaS
   // (the cp.async producer takes any power-of-two page; measured, pages of 8 and 16 keys are faster as TMA boxes:
   // 0.49 / 0.70 of the HBM peak against 0.48 / 0.60)
   a.gather = paged && (kp.page_size == 1 || kp.page_size == 2 || kp.page_size == 4);
-  // rows per TMA box: a page, a whole stage, or (pages that are an odd multiple of 64 keys under 128-key stages) 64
-  a.box_rows = a.gather ? 1 : (!paged ? TNS : (kp.page_size < TNS ? kp.page_size : (kp.page_size % TNS == 0 ? TNS : 64)));
+  // rows per TMA box: a whole stage of contiguous K/V, else a page or 64 rows of a larger page.  (Never more than 64
+  // of a page: a stage starts at a multiple of 64 keys - split and window boundaries are in 64-key blocks - so a
+  // 128-row box of a 128-key stage could start in the middle of a page and run into the physically next one.)
+  a.box_rows = a.gather ? 1 : (!paged ? TNS : (kp.page_size < 64 ? kp.page_size : 64));
   const uint64_t rows = paged ? (uint64_t)kp.num_pages * (uint64_t)kp.page_size : (uint64_t)kp.total_k;
   a.kv_total_rows = (int)rows;
   const int kvdt = KV8 ? FA_DT_FP8_E4M3 : (std::is_same<T, __half>::value ? FA_DT_FP16 : FA_DT_BF16);

@@ -108,6 +108,20 @@ def test_decode_route_gathers_small_pages(page_size, kv_dtype, cuda_device):
     _check(p, cuda_device, AUTO, tol)
 
 
+@pytest.mark.parametrize("page_size", [128, 256])
+def test_e4m3_cache_decode_stage_starting_inside_a_page(page_size, cuda_device):
+    """An e4m3 cache is streamed in 128-key stages, but split and window boundaries fall on 64-key blocks: a stage
+    may start in the middle of a page of 128 or 256 keys, and its rows must still come from the right pages."""
+    p = W.make_problem(f"e4m3_midpage_{page_size}", [(2, 946), (1, 863), (3, 1210)], hq=8, hkv=2, hd=128, dtype="bf16",
+                       kv_dtype="fp8", causal=True, window_left=319, window_right=0, page_size=page_size, seed=58)
+    _check(p, cuda_device, AUTO, 6e-2)
+    _check(p, cuda_device, DEC, 6e-2, num_splits=3)
+    q = W.make_problem(f"e4m3_midpage_split_{page_size}", [(2, 584), (3, 1210)], hq=4, hkv=4, hd=128, dtype="bf16",
+                       kv_dtype="fp8", causal=True, page_size=page_size, seed=59)
+    _check(q, cuda_device, AUTO, 6e-2)
+    _check(q, cuda_device, DEC, 6e-2, num_splits=5)
+
+
 @pytest.mark.parametrize("hd,hdv", [(64, 64), (192, 128)])
 @pytest.mark.parametrize("page_size", [1, 4])
 def test_decode_route_small_pages_other_head_dims(page_size, hd, hdv, cuda_device):
