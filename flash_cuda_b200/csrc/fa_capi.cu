@@ -298,7 +298,13 @@ int fa_b200_fwd(const FaFwdParams* p, void* workspace, size_t workspace_bytes, f
   if (!workspace || workspace_bytes < w.total || ((uintptr_t)workspace % 256)) return FA_ERR_WORKSPACE;
   if (p->total_q == 0 || p->batch == 0) return FA_OK;
 
-  if (p->scheduler_metadata && p->scheduler_metadata_len > 0 && p->scheduler_metadata_len != sched_len(pl, p->batch))
+  // Only the decode and the tensor-core prefill kernels read the metadata; the general kernel has no use for it, and
+  // a list made for one of the other two (the metadata call knows a single element type: 16-bit queries over an
+  // e4m3 cache with many rows are planned there as a tensor-core prefill, here as the general route) is then left
+  // unread rather than refused.
+  const bool md_read = pl.route == FA_ROUTE_DECODE || pl.route == FA_ROUTE_PREFILL_TC;
+  if (md_read && p->scheduler_metadata && p->scheduler_metadata_len > 0 &&
+      p->scheduler_metadata_len != sched_len(pl, p->batch))
     return FA_ERR_BAD_METADATA;
 
   char* ws = (char*)workspace;

@@ -77,7 +77,8 @@ typedef struct FaFwdParams {
   const int32_t* scheduler_metadata; /* output of fa_b200_get_scheduler_metadata for this problem, or NULL.
                                       * The kernels compare its header (batch, tiles, splits, route) with the
                                       * call before they index it; a mismatch ends the call without output and
-                                      * fa_b200_check_status returns FA_ERR_BAD_METADATA. */
+                                      * fa_b200_check_status returns FA_ERR_BAD_METADATA.  Calls that the
+                                      * general kernel serves do not read it at all. */
   /* ---- sizes ---- */
   int32_t batch, total_q, total_k, hq, hkv, hd, hdv;
   int32_t max_seqlen_q, max_seqlen_k;      /* upper bounds known on the host (any upper bound is valid: the

@@ -275,6 +275,16 @@ def test_work_order_by_kv_head(cuda_device):
     assert (base_lse.cpu() - ref_lse).abs().max().item() <= 2e-3
 
 
+def test_metadata_is_left_unread_on_the_general_route(cuda_device):
+    """The metadata call knows one element type.  For 16-bit queries over an e4m3 cache with many query rows it plans
+    a tensor-core prefill, while `fwd` (which sees both types) takes the general kernel: that kernel does not read the
+    list, so the call goes through with it."""
+    p = W.make_problem("md_general", [(169, 437), (192, 840)], hq=8, hkv=1, hd=128, dtype="fp16", kv_dtype="fp8",
+                       causal=False, sink=True, page_size=128, seed=60)
+    md = _metadata_for(p, cuda_device)
+    _check(p, cuda_device, AUTO, 6e-2, scheduler_metadata=md)
+
+
 @pytest.mark.parametrize("kind", ["decode", "prefill"])
 def test_metadata_of_another_problem_is_refused(kind, cuda_device):
     """Metadata built for batch 5 handed to a batch-3 call.  It is long enough that no read could leave the
