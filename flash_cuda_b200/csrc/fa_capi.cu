@@ -487,10 +487,12 @@ int fa_b200_combine_strided(const float* o_part, const float* lse_part, int64_t 
 size_t fa_b200_sizeof_append_params(void) { return sizeof(FaAppendParams); }
 
 int fa_b200_append_kv(const FaAppendParams* p, fa_stream_t stream) {
-  if (!p || !p->k_new || !p->v_new || !p->k_cache || !p->v_cache || !p->cu_seqlens_k_new || !p->seqused_k ||
-      !p->seqused_k_out || !p->page_table || p->seqused_k_out == p->seqused_k)
+  if (!p || !p->k_cache || !p->v_cache || !p->cu_seqlens_k_new || !p->seqused_k || !p->seqused_k_out || !p->page_table ||
+      p->seqused_k_out == p->seqused_k)
     return FA_ERR_BAD_ARG;
   if (p->batch < 0 || p->total_new < 0 || p->hkv <= 0 || p->page_size <= 0) return FA_ERR_BAD_ARG;
+  // (a step that appends no key at all - an empty k_new has no address - still rotates the queries and writes the counts)
+  if (p->total_new > 0 && (!p->k_new || !p->v_new)) return FA_ERR_BAD_ARG;
   const bool kv8 = p->kv_dtype == FA_DT_FP8_E4M3;
   if (p->kv_dtype < 0 || p->kv_dtype > 2 || p->q_dtype < 0 || p->q_dtype > 1) return FA_ERR_UNSUPPORTED;
   const int esz = kv8 ? 1 : 2, epc = 16 / esz;   // elements per 16-byte chunk
@@ -501,7 +503,8 @@ int fa_b200_append_kv(const FaAppendParams* p, fa_stream_t stream) {
   const uintptr_t ptrs[] = {(uintptr_t)p->k_new, (uintptr_t)p->v_new, (uintptr_t)p->k_cache, (uintptr_t)p->v_cache};
   for (uintptr_t a : ptrs) if (a % 16) return FA_ERR_UNSUPPORTED;
   if (p->rotary_cos) {
-    if (!p->rotary_sin || !p->q || !p->q_out || !p->cu_seqlens_q || p->q_out == p->q) return FA_ERR_BAD_ARG;
+    if (!p->rotary_sin || !p->cu_seqlens_q) return FA_ERR_BAD_ARG;
+    if (p->total_q > 0 && (!p->q || !p->q_out || p->q_out == p->q)) return FA_ERR_BAD_ARG;   // (no query rows: no addresses)
     if (kv8 || p->kv_dtype != p->q_dtype) return FA_ERR_UNSUPPORTED;       // keys are rotated in the query type
     if (p->rotary_dim <= 0 || p->rotary_dim % 16 || p->rotary_dim > p->hd || p->hd % 8) return FA_ERR_UNSUPPORTED;
     if (p->q_row_stride % 8 || p->q_head_stride % 8 || p->qo_row_stride % 8 || p->qo_head_stride % 8 ||

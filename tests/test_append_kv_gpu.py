@@ -66,6 +66,27 @@ def test_append_and_rotary_are_bit_exact(dtype, page, hd, rd, interleaved, cuda_
         assert torch.equal(_bits(d["q"].cpu()), _bits(c["q"])), "q itself must not be modified"
 
 
+@pytest.mark.parametrize("used,new,q_lens", [((0, 399), (0, 0), (0, 3)),      # nothing to append, queries still rotate
+                                             ((473,), (11,), (0,)),            # keys appended, no query row at all
+                                             ((0,), (0,), (0,))])              # nothing of either
+def test_append_steps_without_new_keys_or_without_queries(used, new, q_lens, cuda_device):
+    """Empty `k_new` / `q` tensors have no address: the call must take them for what they are."""
+    c = _case(torch.float16, 8, 64, 32, seed=65, hq=4, hkv=4, used=used, new=new, q_lens=q_lens)
+    want_q, want_k, want_v, want_n = append_kv_reference(
+        c["k_new"], c["v_new"], c["k_cache"], c["v_cache"], page_table=c["page_table"], seqused_k=c["seqused_k"],
+        cu_seqlens_k_new=c["cu_seqlens_k_new"], q=c["q"], cu_seqlens_q=c["cu_seqlens_q"], rotary_cos=c["rotary_cos"],
+        rotary_sin=c["rotary_sin"], rotary_interleaved=True, q_positions_advance=False)
+    d = {k: v.to(cuda_device) for k, v in c.items()}
+    q_rot, n_out = capi.append_kv(d["k_new"], d["v_new"], d["k_cache"], d["v_cache"], page_table=d["page_table"],
+                                  seqused_k=d["seqused_k"], cu_seqlens_k_new=d["cu_seqlens_k_new"], q=d["q"],
+                                  cu_seqlens_q=d["cu_seqlens_q"], rotary_cos=d["rotary_cos"], rotary_sin=d["rotary_sin"],
+                                  rotary_interleaved=True, q_positions_advance=False)
+    torch.cuda.synchronize()
+    assert n_out.cpu().tolist() == want_n.tolist()
+    assert torch.equal(_bits(d["k_cache"].cpu()), _bits(want_k)) and torch.equal(_bits(d["v_cache"].cpu()), _bits(want_v))
+    assert torch.equal(_bits(q_rot.cpu()), _bits(want_q))
+
+
 def test_append_without_rotary_into_e4m3_cache_is_a_byte_copy(cuda_device):
     c = _case(torch.bfloat16, 32, 128, 128, seed=62)
     f8 = lambda t: (t.float() * 8).to(torch.float8_e4m3fn)
