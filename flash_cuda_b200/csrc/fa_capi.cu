@@ -222,7 +222,11 @@ static WsLayout ws_layout(const FaFwdParams* p, const Plan& pl) {
 }
 
 static int validate(const FaFwdParams* p) {
-  if (!p || !p->q || !p->k || !p->v || !p->out || !p->lse || !p->cu_seqlens_q) return FA_ERR_BAD_ARG;
+  if (!p || !p->cu_seqlens_q) return FA_ERR_BAD_ARG;
+  // tensors without elements have no address: queries are needed only if there is a query row, keys only if a
+  // contiguous K/V holds a key
+  if (p->total_q > 0 && (!p->q || !p->out || !p->lse)) return FA_ERR_BAD_ARG;
+  if ((p->page_table || p->total_k > 0) && (!p->k || !p->v)) return FA_ERR_BAD_ARG;
   if (p->page_table) {
     if (!p->seqused_k || p->page_size <= 0) return FA_ERR_BAD_ARG;
   } else if (!p->cu_seqlens_k) {
@@ -242,6 +246,18 @@ static int validate(const FaFwdParams* p) {
   const uintptr_t ptrs[] = {(uintptr_t)p->q, (uintptr_t)p->k, (uintptr_t)p->v, (uintptr_t)p->out};
   for (uintptr_t a : ptrs) if (a % 16) return FA_ERR_UNSUPPORTED;
   return FA_OK;
+}
+
+// The call as the kernels get it: unchanged, or (a contiguous K/V without a single key) re-addressed for the
+// general kernel, see fa_b200_fwd.
+static const FaFwdParams* without_keys(const FaFwdParams* p, FaFwdParams* tmp) {
+  if (p->page_table || p->total_k != 0 || p->total_q <= 0 || !p->q) return p;
+  *tmp = *p;
+  tmp->k = tmp->v = p->q;
+  tmp->route = FA_ROUTE_GENERAL;
+  tmp->num_splits = 1;
+  tmp->scheduler_metadata = nullptr;
+  return tmp;
 }
 
 }  // namespace fa
@@ -270,8 +286,10 @@ const char* fa_b200_strerror(int code) {
 }
 const char* fa_b200_last_cuda_error(void) { return g_last_cuda_error; }
 
-size_t fa_b200_fwd_workspace_bytes(const FaFwdParams* p) {
-  if (!p) return 0;
+size_t fa_b200_fwd_workspace_bytes(const FaFwdParams* p_in) {
+  if (!p_in) return 0;
+  FaFwdParams no_keys;
+  const FaFwdParams* p = without_keys(p_in, &no_keys);
   const DevInfo* di = device_info();
   Plan pl = make_plan(plan_input(p, di && di->sms > 0 ? di->sms : 148));
   if (pl.err != FA_OK) return 256;
@@ -285,10 +303,22 @@ int fa_b200_num_splits(const FaFwdParams* p) {
   return pl.err == FA_OK ? pl.nsplits : 1;
 }
 
-int fa_b200_fwd(const FaFwdParams* p, void* workspace, size_t workspace_bytes, fa_stream_t stream_) {
+int fa_b200_fwd(const FaFwdParams* p_in, void* workspace, size_t workspace_bytes, fa_stream_t stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  int rc = validate(p);
+  int rc = validate(p_in);
   if (rc != FA_OK) return rc;
+  // A contiguous K/V without a single key: every row sees nothing (zeros, LSE of the sink alone or -inf).  The
+  // general kernel writes that without touching K or V; it is given the query tensor as a stand-in address.
+  if (p_in->total_q == 0 || p_in->batch == 0) {
+    // no query row: nothing to write, but fa_b200_check_status must find a clean status word afterwards
+    if (workspace && workspace_bytes >= 256 && !(p_in->flags & FA_FLAG_WORKSPACE_CLEAN)) {
+      cudaError_t ce = cudaMemsetAsync(workspace, 0, 256, stream);
+      if (ce != cudaSuccess) return cuda_fail(ce, "cudaMemsetAsync(workspace header)");
+    }
+    return FA_OK;
+  }
+  FaFwdParams no_keys;
+  const FaFwdParams* p = without_keys(p_in, &no_keys);
   const DevInfo* di = device_info();
   if (!di || !di->ok) return FA_ERR_NO_DEVICE;
   PlanInput in = plan_input(p, di->sms);

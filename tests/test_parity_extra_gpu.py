@@ -275,6 +275,24 @@ def test_work_order_by_kv_head(cuda_device):
     assert (base_lse.cpu() - ref_lse).abs().max().item() <= 2e-3
 
 
+@pytest.mark.parametrize("reqs,page", [([(1, 0)], 0), ([(2, 0), (0, 0)], 0), ([(448, 0)], 0),     # K/V without a key
+                                       ([(0, 20)], 4), ([(0, 0), (0, 5)], 16), ([(0, 191)], 256)])  # no query row
+def test_batches_without_keys_or_without_queries(reqs, page, cuda_device):
+    """Tensors without elements have no address.  A contiguous K/V without a single key gives zeros and the LSE of
+    the sink alone (or -inf); a batch without a query row is a call that writes nothing; both leave a clean status."""
+    for sink in (False, True):
+        p = W.make_problem("nothing", reqs, hq=4, hkv=2, hd=128, causal=True, sink=sink, page_size=page, seed=61)
+        ref_out, ref_lse = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
+        pd = p.to(cuda_device)
+        out, lse, _ = capi.fwd(pd.q, pd.k, pd.v, check=True, **pd.capi_kw())
+        assert out.shape == ref_out.shape and lse.shape == ref_lse.shape
+        if out.numel():
+            assert torch.equal(out.float().cpu(), ref_out)              # zeros
+            fin = torch.isfinite(ref_lse)
+            assert torch.equal(torch.isfinite(lse.cpu()), fin)
+            torch.testing.assert_close(lse.cpu()[fin], ref_lse[fin], atol=1e-5, rtol=1e-5)
+
+
 def test_metadata_is_left_unread_on_the_general_route(cuda_device):
     """The metadata call knows one element type.  For 16-bit queries over an e4m3 cache with many query rows it plans
     a tensor-core prefill, while `fwd` (which sees both types) takes the general kernel: that kernel does not read the
