@@ -78,3 +78,53 @@ def test_random_configurations_match_the_oracle(seed, cuda_device):
         if not (err <= tol and lse_err <= 2e-2 and torch.equal(torch.isfinite(lse), fin) and torch.isfinite(out).all()):
             failures.append((n, reqs, kw, extra, err, lse_err))
     assert not failures, failures[:3]
+
+
+def test_random_scheduler_metadata_is_bit_exact(cuda_device):
+    """Integer output: every word of the work list equals the CPU restatement, over random batches of every kind."""
+    from oracle import sched_oracle as SO
+    rng = random.Random(29)
+    sms = torch.cuda.get_device_properties(cuda_device).multi_processor_count
+    code = {torch.bfloat16: SO.DT_BF16, torch.float16: SO.DT_FP16, torch.float8_e4m3fn: SO.DT_FP8}
+    for n in range(250):
+        hd, hdv = rng.choice([(64, 64), (96, 96), (128, 128), (192, 128), (192, 192), (256, 256)])
+        hkv = rng.choice([1, 2, 4, 8])
+        hq = hkv * rng.choice([1, 2, 4, 8])
+        kind = rng.choice(["prefill", "decode", "mixed"])
+        q_lens, k_lens = [], []
+        for _ in range(rng.randint(1, 40)):
+            if kind == "prefill":
+                q = rng.randint(0, 3000)
+                k = q + rng.randint(0, 2000)
+            elif kind == "decode":
+                q, k = rng.randint(0, 4), rng.randint(0, 40000)
+            elif rng.random() < 0.6:
+                q, k = rng.randint(1, 3), rng.randint(1, 9000)
+            else:
+                q = rng.randint(100, 2000)
+                k = q + rng.randint(0, 500)
+            q_lens.append(q)
+            k_lens.append(k)
+        if max(q_lens) == 0:
+            continue
+        page = rng.choice([0, 1, 4, 8, 16, 64, 128, 256])
+        leftpad = [rng.randint(0, max(0, k - 1)) for k in k_lens] if (page and rng.random() < 0.3) else None
+        causal = rng.random() < 0.8
+        wl = rng.choice([-1, -1, rng.randint(0, 3000)])
+        wr = -1 if (causal or wl < 0) else rng.choice([-1, rng.randint(0, 100)])
+        if causal and wl >= 0:
+            wr = 0
+        ns = rng.choice([0, 0, 1, 3, 8])
+        dtype = rng.choice([torch.bfloat16, torch.float16] + ([torch.float8_e4m3fn] if hd == 128 else []))
+        shape = dict(batch=len(q_lens), max_seqlen_q=max(q_lens), max_seqlen_k=max(max(k_lens), 1), hq=hq, hkv=hkv, hd=hd,
+                     hdv=hdv, page_size=page)
+        cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=cuda_device)
+        md = capi.get_scheduler_metadata(
+            cuda_device, dtype=dtype, seqused_k=torch.tensor(k_lens, dtype=torch.int32, device=cuda_device), cu_seqlens_q=cu_q,
+            leftpad_k=None if leftpad is None else torch.tensor(leftpad, dtype=torch.int32, device=cuda_device),
+            causal=causal, window_left=wl, window_right=wr, num_splits=ns, **shape)
+        plan = SO.make_plan(num_sms_device=sms, q_dtype=code[dtype], num_splits=ns, **shape)
+        want = SO.scheduler_metadata(plan, batch=len(q_lens), max_seqlen_q=shape["max_seqlen_q"],
+                                     max_seqlen_k=shape["max_seqlen_k"], q_lens=q_lens, k_lens=k_lens, leftpad=leftpad,
+                                     causal=causal, window_left=wl, window_right=wr)
+        assert md.cpu().tolist() == want, (n, shape, causal, wl, wr, ns, dtype)
