@@ -91,3 +91,36 @@ def test_scheduler_metadata_round_trip(cuda_device):
         d["k"].shape[1], 0, True, -1, -1, False, int(cfg["num_splits"]), None, 0)
     with pytest.raises(RuntimeError, match="scheduler_metadata"):
         ops.fwd(*_golden.fwd_args(d, cuda_device, scheduler_metadata=other))
+
+
+@pytest.mark.parametrize("kind", ["decode", "decode_e4m3", "prefill", "mixed"])
+def test_fwd_op_is_captured_in_a_cuda_graph_and_replayed(kind, cuda_device):
+    """The serving path launches decode steps from CUDA graphs: after a warm-up (the op's per-stream workspace
+    exists) a call is captured, replayed into a cleared output, and gives the oracle's numbers.  No allocation,
+    synchronisation or host read happens inside the call."""
+    from flash_cuda_b200 import workloads as W
+    from oracle.ref_attention import ref_attention
+    p = {"decode": lambda: W.make_problem("g_dec", [(1, 3000), (1, 700), (2, 5000)], hq=8, hkv=2, hd=128, page_size=64, seed=1),
+         "decode_e4m3": lambda: W.make_problem("g_dec8", [(1, 3000), (1, 700)], hq=8, hkv=2, hd=128, page_size=16,
+                                               kv_dtype="fp8", seed=2),
+         "prefill": lambda: W.make_problem("g_pre", [(500, 500), (300, 900)], hq=8, hkv=2, hd=128, seed=3),
+         "mixed": lambda: W.make_problem("g_mix", [(1, 900), (400, 400), (2, 100)], hq=8, hkv=2, hd=128, page_size=64,
+                                         seed=4)}[kind]()
+    ref_out, _ = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
+    pd = p.to(cuda_device)
+    kw = {k: v for k, v in pd.capi_kw().items()}
+    out = torch.empty(pd.q.shape[0], pd.q.shape[1], pd.v.shape[-1], device=cuda_device, dtype=pd.q.dtype)
+    s = torch.cuda.Stream(device=cuda_device)
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            ops.call_fwd(pd.q, pd.k, pd.v, out=out, **kw)
+    s.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        ops.call_fwd(pd.q, pd.k, pd.v, out=out, **kw)
+    out.zero_()
+    g.replay()
+    g.replay()
+    torch.cuda.synchronize()
+    tol = 6e-2 if kind == "decode_e4m3" else 2e-2
+    assert (out.float().cpu() - ref_out).abs().max().item() <= tol
