@@ -72,8 +72,8 @@ struct TcArgs {
   int use_list;      // kp.work holds scheduler metadata of this route: items = its valid entries x hq
   int head_major;    // arithmetic order: all tiles of one (batch, kv head) are consecutive ids (K/V larger than L2)
   int stage_out;     // map_o is valid: full 32-row groups leave through shared memory and TMA stores
-  int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128); 1 in gather mode
-  int gather;        // pages of 1, 2 or 4 keys: K/V maps are 2-D with one-row boxes, rows come four per tile::gather4
+  int kv_box_rows;   // rows per K/V TMA box: 128 (contiguous KV) or min(page_size, 128)
+  int gather;        // pages of 1, 2 or 4 keys: K/V rows are copied with cp.async (the K/V maps are not used)
   int kv_total_rows; // rows of the K/V tensor map (out-of-range y => zero fill)
   int out_cols;      // value columns that exist (head_dim 96 runs as 128 with zero-filled columns 96..127)
 };
@@ -201,8 +201,8 @@ struct Ring {
 // Paged K/V tiles.  The TMA boxes of a 128-key tile (one page each, or 128 keys of a larger page) are shared out
 // j = j0, j0 + jstride, ..: j0 = lane, jstride = 32 when the whole warp produces (every lane owns one box), 0 and 1
 // when lane 0 produces alone (pages of >= 64 keys then: at most two boxes).  With pages of 1, 2 or 4 keys (whole
-// warp only) lane g owns keys 4g .. 4g+3 and fetches them with one tile::gather4 per 128-byte column block (2-D
-// maps over [rows][heads x head_dim] then).  Either way a lane's share of a tile is at most four pool rows.
+// warp only) lane g looks up the pool rows of keys g, g + 32, g + 64, g + 96 and the warp copies the tile row by row
+// with cp.async (copy_tile_rows).  Either way a lane's share of a tile is at most four pool rows.
 struct PageRows { int y[4]; };
 
 // The pool rows of key block nb.  K and V share the page table, so one look-up serves K(nb) and V(nb); it is made a
@@ -216,7 +216,7 @@ __device__ __forceinline__ PageRows page_rows(const TcArgs& a, int nb, int b, in
   if (a.gather) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int kk = nb * TN + 4 * lane + j;
+      const int kk = nb * TN + lane + 32 * j;
       pr.y[j] = 0;               // beyond the sequence: pool row 0 (finite by contract), masked by the softmax
       if (kk < seqlen_k) {
         const int lp = kk >> p.page_shift;
@@ -244,17 +244,64 @@ template <int EPB>
 __device__ __forceinline__ void load_tile_paged(const TcArgs& a, const CUtensorMap* map, int width, uint32_t dst, uint32_t bar,
                                              int hk, int r0, int rstride, int y0, int y1, int y2, int y3) {
   const int ncb = width / EPB;
-  if (a.gather) {
-#pragma unroll 1
-    for (int cb = 0; cb < ncb; ++cb)
-      tma_gather4_2d(dst + cb * (TN * 128) + r0 * 128, map, hk * width + cb * EPB, y0, y1, y2, y3, bar);
-    return;
-  }
 #pragma unroll 1
   for (int i = 0, r = r0; i < 4 && r < TN; ++i, r += rstride) {
     const int y = i == 0 ? y0 : (i == 1 ? y1 : (i == 2 ? y2 : y3));
 #pragma unroll 1
     for (int cb = 0; cb < ncb; ++cb) tma_load_3d(dst + cb * (TN * 128) + r * 128, map, cb * EPB, hk, y, bar);
+  }
+}
+
+// One K or V tile of a cache in pages of 1, 2 or 4 keys, by the whole producer warp with cp.async: the tile's 16-byte
+// chunks in row order, CPR consecutive lanes on one row, each written where a 128-byte-swizzled TMA box would have
+// put it (column block ch / 8, row r, chunk (ch % 8) ^ (r % 8)).  Row r comes from pool row y[r / 32] of lane
+// r % 32.  The TMA unit retires about one copy per 100 cycles whatever its size (128 four-row gathers per key
+// block: 401 TFLOP/s); these copies take the load/store path.  Rolled, eight copies per turn with their row
+// numbers fetched first (a shuffle followed at once by its copy would cost the shuffle's latency per copy).
+template <int CPR>
+__device__ __forceinline__ void copy_tile_rows(uint32_t dst0, const unsigned char* src0, uint32_t pitch, const PageRows& pr,
+                                               int lane) {
+  if constexpr (32 % CPR == 0) {
+    // RPI rows per instruction; row r = i * RPI + hb, and (r & 7) = ((i * RPI) & 7) ^ hb because the low bits of
+    // i * RPI are clear
+    constexpr int RPI = 32 / CPR;
+    const int hb = lane / CPR, ch = lane - hb * CPR;
+    const uint32_t dl = dst0 + (uint32_t)(ch >> 3) * (TN * 128) + (uint32_t)hb * 128u;
+    const uint32_t xs = (uint32_t)(((ch & 7) ^ hb) << 4);
+    const unsigned char* sl = src0 + ch * 16;
+#pragma unroll 1
+    for (int i0 = 0; i0 < TN / RPI; i0 += 8) {
+      const int quarter = (i0 * RPI) >> 5;      // the eight copies of a turn take rows of one quarter of the tile
+      const int yv = quarter == 0 ? pr.y[0] : (quarter == 1 ? pr.y[1] : (quarter == 2 ? pr.y[2] : pr.y[3]));
+      int y[8];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) y[g] = __shfl_sync(0xffffffffu, yv, (((i0 + g) * RPI) & 31) + hb);
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const int r0 = (i0 + g) * RPI;
+        cp_async16(dl + (uint32_t)r0 * 128u + (xs ^ (uint32_t)((r0 & 7) << 4)), sl + (uint64_t)(uint32_t)y[g] * pitch, 16u);
+      }
+    }
+  } else {
+    constexpr int N = TN * CPR / 32;
+    static_assert(N % 8 == 0, "whole turns");
+#pragma unroll 1
+    for (int i0 = 0; i0 < N; i0 += 8) {
+      int y[8];
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const int r = ((i0 + g) * 32 + lane) / CPR;
+        const int quarter = (((i0 + g) * 32) / CPR) >> 5;      // the same for every lane of one instruction
+        const int yv = quarter == 0 ? pr.y[0] : (quarter == 1 ? pr.y[1] : (quarter == 2 ? pr.y[2] : pr.y[3]));
+        y[g] = __shfl_sync(0xffffffffu, yv, r & 31);
+      }
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const int q = (i0 + g) * 32 + lane, r = q / CPR, ch = q - r * CPR;
+        cp_async16(dst0 + (uint32_t)(ch >> 3) * (TN * 128) + (uint32_t)r * 128u + (uint32_t)(((ch & 7) ^ (r & 7)) << 4),
+                   src0 + (uint64_t)(uint32_t)y[g] * pitch + ch * 16, 16u);
+      }
+    }
   }
 }
 
@@ -316,14 +363,17 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
   if (tid == 0) {
     for (int t = 0; t < 2; ++t) { mbar_init(bar_q_full + 8 * t, 1); mbar_init(bar_q_empty + 8 * t, 1); }
     for (int s = 0; s < KST; ++s) mbar_init(bar_k_empty + 8 * s, 1);
-    for (int s = 0; s < VST; ++s) { mbar_init(bar_v_full + 8 * s, 1); mbar_init(bar_v_empty + 8 * s, 1); }
+    // (rows copied with cp.async: a tile completes on one arrival per producer lane when its copies have landed, plus
+    // lane 0's own)
+    const int full_cnt = (PROD == 2 && a.gather) ? 33 : 1;
+    for (int s = 0; s < VST; ++s) { mbar_init(bar_v_full + 8 * s, full_cnt); mbar_init(bar_v_empty + 8 * s, 1); }
     for (int t = 0; t < 2; ++t) {
       mbar_init(bar_s_full + 8 * t, 1); mbar_init(bar_p_full + 8 * t, 4);     // one elected arrival per softmax warp
       mbar_init(bar_o_full + 8 * t, 1); mbar_init(bar_o_empty + 8 * t, 4);
     }
     mbar_init(bar_drain, 1);
-    mbar_init(bar_k0_full, 1);
-    for (int s = 0; s < KST; ++s) mbar_init(bar_k_full + 8 * s, 1);
+    mbar_init(bar_k0_full, full_cnt);
+    for (int s = 0; s < KST; ++s) mbar_init(bar_k_full + 8 * s, full_cnt);
     for (int i = 0; i < 2; ++i) { mbar_init(bar_w_full + 8 * i, 1); mbar_init(bar_w_empty + 8 * i, 1 + 4 * NTL); }
     s_abort[0] = 0;
     s_abort[1] = 0;   // [1] is never raised: waits that may only end by completion or time limit
@@ -438,10 +488,22 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         const int hk = it.h / p.rep;
         // one K or V tile of key block nb into `dst`, completing on `bar`
         const int pj0 = wide ? lane : 0, pjs = wide ? 32 : 1;
-        // first row of this lane's first box and the distance to its next one (gather: four rows per lane)
-        const int pr0 = a.gather ? 4 * lane : pj0 * a.kv_box_rows, prs = pjs * a.kv_box_rows;
+        // first row of this lane's first box and the distance to its next one
+        const int pr0 = pj0 * a.kv_box_rows, prs = pjs * a.kv_box_rows;
+        const bool cpg = wide && a.gather;      // pages of 1, 2, 4 keys: rows by cp.async, completion by arrivals
+        auto open_bar = [&](uint32_t bar, uint32_t bytes) {
+          if (leader) { if (cpg) mbar_arrive(bar); else mbar_expect_tx(bar, bytes); }
+        };
+        auto close_bar = [&](uint32_t bar) { if (cpg) cp_async_arrive_noinc(bar); };
         auto load_tile = [&](const CUtensorMap* map, int width, uint32_t dst, int nb, uint32_t bar, const PageRows& pr) {
-          if (!paged) {
+          if (cpg) {
+            if (map == &map_k)
+              copy_tile_rows<HD * ESZ / 16>(dst, reinterpret_cast<const unsigned char*>(p.k) + (int64_t)hk * HD * ESZ,
+                                            (uint32_t)(p.k_row_stride * ESZ), pr, lane);
+            else
+              copy_tile_rows<HDV * ESZ / 16>(dst, reinterpret_cast<const unsigned char*>(p.v) + (int64_t)hk * HDV * ESZ,
+                                             (uint32_t)(p.v_row_stride * ESZ), pr, lane);
+          } else if (!paged) {
             if (leader) {
               for (int cb = 0; cb < width / EPB; ++cb)
                 tma_load_3d(dst + cb * (TN * 128), map, cb * EPB, hk, it.k0 + nb * TN, bar);
@@ -459,8 +521,9 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
           ok = lead_wait(bar_k_empty + 8 * s, kr.phase ^ 1u);
           if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
           const uint32_t kbar = MERGE_KV ? bar_k0_full : bar_k_full + 8 * s;
-          if (leader) mbar_expect_tx(kbar, SM::kKStage);
+          open_bar(kbar, SM::kKStage);
           load_tile(&map_k, HD, sK + s * SM::kKStage, it.ulo, kbar, rows_cur);
+          close_bar(kbar);
           kr.advance();
           ++k0cnt;
         }
@@ -477,15 +540,18 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
           ok = lead_wait(bar_v_empty + 8 * vs, vr.phase ^ 1u);
           if (ok && nxt) ok = lead_wait(bar_k_empty + 8 * ks, kr.phase ^ 1u);
           if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
-          if (leader) mbar_expect_tx(bar_v_full + 8 * vs, SM::kVStage + ((MERGE_KV && nxt) ? SM::kKStage : 0));
+          open_bar(bar_v_full + 8 * vs, SM::kVStage + ((MERGE_KV && nxt) ? SM::kKStage : 0));
           load_tile(&map_v, HDV, sV + vs * SM::kVStage, nb, bar_v_full + 8 * vs, rows_cur);
+          if constexpr (!MERGE_KV) close_bar(bar_v_full + 8 * vs);
           vr.advance();
           if (nxt) {
             const uint32_t kbar = MERGE_KV ? bar_v_full + 8 * vs : bar_k_full + 8 * ks;
-            if constexpr (!MERGE_KV) { if (leader) mbar_expect_tx(kbar, SM::kKStage); }
+            if constexpr (!MERGE_KV) open_bar(kbar, SM::kKStage);
             load_tile(&map_k, HD, sK + ks * SM::kKStage, nb + 1, kbar, rows_nxt);
+            if constexpr (!MERGE_KV) close_bar(kbar);
             kr.advance();
           }
+          if constexpr (MERGE_KV) close_bar(bar_v_full + 8 * vs);
           rows_cur = rows_nxt;
           if (nb == it.ulo) it_next = fetch_and_publish();
         }
@@ -542,6 +608,12 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         report_error(p.status, DEV_ERR_TIMEOUT, ROLE_MMA);
         *s_abort = 1;
       }
+    };
+    // a K / V tile has landed.  Tiles copied with cp.async were written through the generic proxy; the MMAs read
+    // shared memory through the async proxy, so a proxy fence stands between the two.
+    auto wait_tile = [&](uint32_t bar, uint32_t parity) {
+      wait(bar, parity);
+      if constexpr (PROD == 2) { if (a.gather) fence_proxy_async_smem(); }
     };
     const uint64_t qd0 = umma_desc(sQ, 16, 1024), kd0 = umma_desc(sK, 16, 1024), vd0 = umma_desc(sV, TN * 128, 1024);
 
@@ -603,8 +675,8 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
       // prologue: QK of the first block
       {
         const uint32_t ks = kr.slot;
-        if constexpr (MERGE_KV) wait(bar_k0_full, k0cnt & 1);
-        else wait(bar_k_full + 8 * ks, kr.phase);
+        if constexpr (MERGE_KV) wait_tile(bar_k0_full, k0cnt & 1);
+        else wait_tile(bar_k_full + 8 * ks, kr.phase);
         ++k0cnt;
 #pragma unroll
         for (int t = 0; t < NTL; ++t) {
@@ -621,7 +693,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         const bool nxt = i + 1 < uhi;
         const uint32_t vs = vr.slot;
         const uint32_t ks = kr.slot;          // slot of block i+1 (if any)
-        wait(bar_v_full + 8 * vs, vr.phase);   // V of this block (and, with merged barriers, K of the next one)
+        wait_tile(bar_v_full + 8 * vs, vr.phase);   // V of this block (and, with merged barriers, K of the next one)
         bool k_ready = MERGE_KV;
 #pragma unroll
         for (int t = 0; t < NTL; ++t) {
@@ -638,7 +710,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
             if (i + 1 == hi[t]) commit(bar_o_full + 8 * t);
           }
           if (nxt && i + 1 >= lo[t] && i + 1 < hi[t]) {
-            if (!k_ready) { wait(bar_k_full + 8 * ks, kr.phase); k_ready = true; }
+            if (!k_ready) { wait_tile(bar_k_full + 8 * ks, kr.phase); k_ready = true; }
             issue_qk(t, ks);
             // tile t's last QK of the item: its Q slot is refilled during the item's remaining blocks
             if (i + 2 == hi[t]) commit(bar_q_empty + 8 * t);
@@ -647,7 +719,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         commit(bar_v_empty + 8 * vs);
         vr.advance();
         if (nxt) {
-          if (!k_ready) wait(bar_k_full + 8 * ks, kr.phase);   // block i+1 belongs to neither tile: still consume its K slot
+          if (!k_ready) wait_tile(bar_k_full + 8 * ks, kr.phase);   // block i+1 belongs to neither tile: still consume its K slot
           commit(bar_k_empty + 8 * ks);
           kr.advance();
         }
@@ -1194,9 +1266,9 @@ struct MapCache {
 };
 
 static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t rows, uint64_t heads, uint64_t head_dim,
-                        uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_rows, int rank = 3) {
+                        uint64_t head_stride_elems, uint64_t row_stride_elems, uint32_t box_rows) {
   static thread_local MapCache cache;
-  const MapKey k{ptr, rows, heads, head_dim, head_stride_elems, row_stride_elems, box_rows, dtype + 16 * rank};
+  const MapKey k{ptr, rows, heads, head_dim, head_stride_elems, row_stride_elems, box_rows, dtype};
   for (int i = 0; i < MapCache::N; ++i)
     if (cache.used[i] && cache.key[i] == k) { *m = cache.map[i]; return true; }
   EncodeTiledFn fn = get_encode_fn();
@@ -1209,19 +1281,9 @@ static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t row
   const CUtensorMapDataType dt = dtype == FA_DT_FP8_E4M3 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : dtype == FA_DT_FP16   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  bool good;
-  if (rank == 2) {     // [rows][columns], columns innermost
-    const cuuint64_t dims2[2] = {head_dim, rows};
-    const cuuint64_t strides2[1] = {row_stride_elems * esz};
-    const cuuint32_t box2[2] = {128 / esz, box_rows};
-    good = fn(m, dt, 2, const_cast<void*>(ptr), dims2, strides2, box2, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-  } else {
-    good = fn(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-  }
+  const bool good = fn(m, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                       CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
   if (!good) return false;
   const int slot = cache.next;
   cache.next = (cache.next + 1) % MapCache::N;
@@ -1231,7 +1293,7 @@ static bool make_map_3d(CUtensorMap* m, const void* ptr, int dtype, uint64_t row
   return true;
 }
 
-// The whole warp produces where a tile is many boxes (pages of <= 32 keys, gathered rows) and, on pages of 64 keys,
+// The whole warp produces where a tile is many boxes or many rows (pages of <= 32 keys) and, on pages of 64 keys,
 // where K rides on V's barrier (equal ring depths: measured 1034 -> 1055 TFLOP/s, 1078 -> 1135 on a 1024-row chunk
 // over 32768 keys); lane 0 alone otherwise (a tile of a page of >= 128 keys is one box: 1143 against 1117 wide).
 template <int KST, int VST>
@@ -1262,15 +1324,8 @@ static int launch_prod(const KParams& kp, const Plan& pl, int dtype, uint64_t kv
   a.out_cols = kp.hdv;
   CUtensorMap mq, mk, mv, mo;
   if (!make_map_3d(&mq, kp.q, dtype, (uint64_t)kp.total_q, kp.hq, kp.hd, kp.hd, (uint64_t)kp.q_row_stride, TM)) return -1;
-  if (a.gather) {
-    // 2-D views [rows][hkv * head_dim] with one-row boxes (tile::gather4 wants a 2-D map whose box has one row):
-    // expressed through the 3-D encoder as one "head" of hkv * head_dim columns
-    if (!make_map_3d(&mk, kp.k, dtype, kv_rows, 1, (uint64_t)kp.hkv * kp.hd, (uint64_t)kp.hkv * kp.hd, (uint64_t)kp.k_row_stride, 1, 2)) return -1;
-    if (!make_map_3d(&mv, kp.v, dtype, kv_rows, 1, (uint64_t)kp.hkv * kp.hdv, (uint64_t)kp.hkv * kp.hdv, (uint64_t)kp.v_row_stride, 1, 2)) return -1;
-  } else {
-    if (!make_map_3d(&mk, kp.k, dtype, kv_rows, kp.hkv, kp.hd, kp.hd, (uint64_t)kp.k_row_stride, a.kv_box_rows)) return -1;
-    if (!make_map_3d(&mv, kp.v, dtype, kv_rows, kp.hkv, kp.hdv, kp.hdv, (uint64_t)kp.v_row_stride, a.kv_box_rows)) return -1;
-  }
+  if (!make_map_3d(&mk, kp.k, dtype, kv_rows, kp.hkv, kp.hd, kp.hd, (uint64_t)kp.k_row_stride, a.kv_box_rows)) return -1;
+  if (!make_map_3d(&mv, kp.v, dtype, kv_rows, kp.hkv, kp.hdv, kp.hdv, (uint64_t)kp.v_row_stride, a.kv_box_rows)) return -1;
   // output map (16-bit element type of the output): 64 columns x 32 rows per store.  A layout TMA cannot describe
   // only switches the staged path off.
   a.stage_out = 0;
@@ -1327,7 +1382,7 @@ bool prefill_tc_supported(const PlanInput& in) {
   if (in.q_dtype == FA_DT_FP8_E4M3 && !(in.hd == 128 && in.hdv == 128)) return false;   // e4m3: head_dim 128 only
   if (in.page_size > 0) {
     const int ps = in.page_size;
-    const bool gather = (ps == 1 || ps == 2 || ps == 4) && in.hd != 96;   // four rows per tile::gather4 (2-D maps: no zero-filled columns)
+    const bool gather = (ps == 1 || ps == 2 || ps == 4) && in.hd != 96;   // rows by cp.async (whole rows: no zero-filled columns)
     if (!gather && (ps % 8 != 0 || !((128 % ps == 0) || (ps % 128 == 0)))) return false;
   }
   return in.hkv > 0 && in.hq % in.hkv == 0;

@@ -135,16 +135,6 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, int x
       : "memory");
 }
 
-// Four single rows y0..y3 of a 2-D tensor (box [128 bytes, 1 row]) into four consecutive 128-byte rows of shared
-// memory.  The 128-byte swizzle is applied by absolute shared-memory offset, so rows gathered to row 4g..4g+3 of a
-// 1024-byte-aligned tile land where a whole-tile load would have put them.
-__device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const void* map, int x, int y0, int y1, int y2, int y3,
-                                               uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.tile::gather4.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y0), "r"(y1), "r"(y2), "r"(y3), "r"(bar)
-      : "memory");
-}
 // 3-D tiled store shared -> global (bulk async group of the issuing thread).  x * elem_size must be a multiple of
 // 16 bytes and no coordinate may be negative; elements outside the tensor are not written.
 __device__ __forceinline__ void tma_store_3d(const void* map, uint32_t src, int x, int y, int z) {

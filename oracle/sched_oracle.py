@@ -84,7 +84,7 @@ def prefill_tc_supported(*, hq, hkv, hd, hdv, q_dtype, kv_dtype, page_size) -> b
         return False
     if q_dtype == DT_FP8 and (hd, hdv) != (128, 128):
         return False
-    gather = page_size in (1, 2, 4) and hd != 96      # rows fetched four at a time
+    gather = page_size in (1, 2, 4) and hd != 96      # rows copied with cp.async
     if page_size and not gather and not (page_size % 8 == 0 and (128 % page_size == 0 or page_size % 128 == 0)):
         return False
     return hq % hkv == 0
