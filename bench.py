@@ -698,7 +698,7 @@ def run_longctx(args) -> None:
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-kernel"])
     ap.add_argument("--ab-shapes", default=",".join(AB_SHAPES), help="--impl reference-kernel: shapes to compare")
