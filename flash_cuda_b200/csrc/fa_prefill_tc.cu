@@ -104,7 +104,7 @@ struct Smem {
   static constexpr bool kStageOut = kRings + kStageBytes + 3 * 1024 <= kSmemLimit;
   static constexpr int kStageOff = kRings;
   static constexpr int kBarOff = kRings + (kStageOut ? kStageBytes : 0);
-  static constexpr int kNumBars = 4 + KST + 2 * VST + 8 + 1 + 4 + 1 + KST;
+  static constexpr int kNumBars = 4 + KST + 2 * VST + 8 + 1 + 4 + 1 + KST + 1;
   static constexpr int kItemOff = kBarOff + ((kNumBars * 8 + 16 + 15) & ~15);   // after abort flags and TMEM base
   static constexpr int kBytes = kItemOff + 2 * 64;             // two mailbox slots of one decoded work item each
 };
@@ -350,10 +350,19 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
   const uint32_t bar_w_empty = bar_w_full + 16;          // [2] read by the MMA thread and the 8 softmax warps
   const uint32_t bar_k0_full = bar_w_empty + 16;         // K of an item's first block (later K tiles ride on v_full)
   const uint32_t bar_k_full = bar_k0_full + 8;           // [KST] used instead when the K and V rings differ in depth
+  const uint32_t bar_pv_done = bar_k_full + 8 * KST;     // one-tile kernels: the PV of a block has run
   // With rings of equal depth a later K tile completes on the barrier of the V tile before it (one consumer wait per
   // block less).  With a single V stage (head_dim 192) that V tile is the late one, and PV must not wait for the
   // K tile behind it as well: there every K tile has the barrier of its slot.
-  constexpr bool MERGE_KV = KST == VST;
+  constexpr bool MERGE_KV = KST == VST && NTL == 2;
+  // One-tile kernels (SDB): the 128 TMEM columns that a second tile's S would take hold a SECOND S buffer of the one
+  // tile instead.  QK(i+1) then does not have to wait for PV(i) (P(i) overlays S(i), in the other buffer): it is issued
+  // a block ahead, the softmax of block i+1 starts the moment block i is done, and the chain per block shrinks from
+  // PV -> QK -> softmax -> PV to max(PV -> load of the single V stage, softmax) -> PV.  Buffers alternate block by
+  // block across items; buffer b has s_full / p_full barrier b (the second tile's, unused in these kernels).
+  constexpr bool SDB = NTL == 1;
+  constexpr uint32_t S1_COL = 384;                       // second S buffer: behind O (128 + up to 256 columns)
+  static_assert(!SDB || NTL * TN + HDV <= S1_COL, "O must end before the second S buffer");
   Item* s_item = reinterpret_cast<Item*>(sm + SM::kItemOff);   // [2]
   volatile int* s_abort = reinterpret_cast<volatile int*>(sm + SM::kBarOff + SM::kNumBars * 8);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(sm + SM::kBarOff + SM::kNumBars * 8 + 8);
@@ -374,6 +383,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
     mbar_init(bar_drain, 1);
     mbar_init(bar_k0_full, full_cnt);
     for (int s = 0; s < KST; ++s) mbar_init(bar_k_full + 8 * s, full_cnt);
+    mbar_init(bar_pv_done, 1);
     for (int i = 0; i < 2; ++i) { mbar_init(bar_w_full + 8 * i, 1); mbar_init(bar_w_empty + 8 * i, 1 + 4 * NTL); }
     s_abort[0] = 0;
     s_abort[1] = 0;   // [1] is never raised: waits that may only end by completion or time limit
@@ -537,21 +547,37 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
           const uint32_t vs = vr.slot, ks = kr.slot;
           PageRows rows_nxt = rows_cur;
           if (paged && nxt) rows_nxt = page_rows(a, nb + 1, it.b, it.seqlen_k, lane, pj0, pjs);
-          ok = lead_wait(bar_v_empty + 8 * vs, vr.phase ^ 1u);
-          if (ok && nxt) ok = lead_wait(bar_k_empty + 8 * ks, kr.phase ^ 1u);
-          if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
-          open_bar(bar_v_full + 8 * vs, SM::kVStage + ((MERGE_KV && nxt) ? SM::kKStage : 0));
-          load_tile(&map_v, HDV, sV + vs * SM::kVStage, nb, bar_v_full + 8 * vs, rows_cur);
-          if constexpr (!MERGE_KV) close_bar(bar_v_full + 8 * vs);
-          vr.advance();
-          if (nxt) {
-            const uint32_t kbar = MERGE_KV ? bar_v_full + 8 * vs : bar_k_full + 8 * ks;
-            if constexpr (!MERGE_KV) open_bar(kbar, SM::kKStage);
-            load_tile(&map_k, HD, sK + ks * SM::kKStage, nb + 1, kbar, rows_nxt);
-            if constexpr (!MERGE_KV) close_bar(kbar);
-            kr.advance();
+          if constexpr (!MERGE_KV) {
+            // separate barriers: K of the next block goes out as soon as its slot is free, without waiting for the
+            // (single) V stage, which is released a whole PV later
+            if (nxt) {
+              ok = lead_wait(bar_k_empty + 8 * ks, kr.phase ^ 1u);
+              if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+              const uint32_t kbar = bar_k_full + 8 * ks;
+              open_bar(kbar, SM::kKStage);
+              load_tile(&map_k, HD, sK + ks * SM::kKStage, nb + 1, kbar, rows_nxt);
+              close_bar(kbar);
+              kr.advance();
+            }
+            ok = lead_wait(bar_v_empty + 8 * vs, vr.phase ^ 1u);
+            if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+            open_bar(bar_v_full + 8 * vs, SM::kVStage);
+            load_tile(&map_v, HDV, sV + vs * SM::kVStage, nb, bar_v_full + 8 * vs, rows_cur);
+            close_bar(bar_v_full + 8 * vs);
+            vr.advance();
+          } else {
+            ok = lead_wait(bar_v_empty + 8 * vs, vr.phase ^ 1u);
+            if (ok && nxt) ok = lead_wait(bar_k_empty + 8 * ks, kr.phase ^ 1u);
+            if (!ok) { if (leader) report_error(p.status, DEV_ERR_TIMEOUT, ROLE_TMA); break; }
+            open_bar(bar_v_full + 8 * vs, SM::kVStage + (nxt ? SM::kKStage : 0));
+            load_tile(&map_v, HDV, sV + vs * SM::kVStage, nb, bar_v_full + 8 * vs, rows_cur);
+            vr.advance();
+            if (nxt) {
+              load_tile(&map_k, HD, sK + ks * SM::kKStage, nb + 1, bar_v_full + 8 * vs, rows_nxt);
+              kr.advance();
+            }
+            close_bar(bar_v_full + 8 * vs);
           }
-          if constexpr (MERGE_KV) close_bar(bar_v_full + 8 * vs);
           rows_cur = rows_nxt;
           if (nb == it.ulo) it_next = fetch_and_publish();
         }
@@ -595,6 +621,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
     const uint32_t tmem_u = __shfl_sync(FULL, tmem, 0);
     const bool leader = elect_one();   // the same lane every time; decided once
     uint32_t qcnt = 0, k0cnt = 0, pcnt[2] = {0, 0}, oecnt[2] = {0, 0};
+    uint32_t qkn = 0, pvn = 0;   // one-tile kernels: QKs / PVs issued so far (buffer = count & 1)
     Ring<KST> kr;
     Ring<VST> vr;
     // A wait that runs out does not branch out of the loops (that would make every loop-carried value
@@ -617,7 +644,8 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
     };
     const uint64_t qd0 = umma_desc(sQ, 16, 1024), kd0 = umma_desc(sK, 16, 1024), vd0 = umma_desc(sV, TN * 128, 1024);
 
-    auto issue_qk = [&](int t, uint32_t kslot) {
+    // S of tile t into TMEM column `col`, completion on `bar`
+    auto issue_qk_to = [&](int t, uint32_t kslot, uint32_t col, uint32_t bar) {
       const uint64_t qd = qd0 + (uint64_t)(t * ((TM * HD * ESZ) >> 4));
       const uint64_t kd = kd0 + (uint64_t)(kslot * (SM::kKStage >> 4));
       if (leader) {
@@ -625,24 +653,26 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         for (int ks = 0; ks < HD / KEL; ++ks) {
           constexpr int kBlk = (TM * 128) >> 4;
           const uint64_t off = (uint64_t)((ks >> 2) * kBlk + (ks & 3) * 2);   // 4 steps of 32 bytes per 128-byte row
-          umma_ss<F8>(tmem_u + t * TN, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
+          umma_ss<F8>(tmem_u + col, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
         }
-        umma_commit(bar_s_full + 8 * t);
+        umma_commit(bar);
       }
     };
+    auto issue_qk = [&](int t, uint32_t kslot) { issue_qk_to(t, kslot, t * TN, bar_s_full + 8 * t); };
     // two_term (e4m3 only): P was written as P_hi (columns 0..31 of S_t) + P_lo (columns 32..63), see the softmax role
-    auto issue_pv = [&](int t, uint32_t vslot, bool first, bool two_term) {
+    auto issue_pv = [&](int t, uint32_t vslot, bool first, bool two_term, uint32_t pcol = 0xffffffffu) {
+      if (pcol == 0xffffffffu) pcol = t * TN;      // P overlays the S it came from
       const uint64_t vd = vd0 + (uint64_t)(vslot * (SM::kVStage >> 4));
       if (leader) {
 #pragma unroll
         for (int ks = 0; ks < TN / KEL; ++ks)   // KEL keys per step = KEL rows of 128 bytes; P: 8 TMEM columns per step
-          umma_ts<F8>(tmem_u + O_BASE + t * O_STRIDE, tmem_u + t * TN + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
+          umma_ts<F8>(tmem_u + O_BASE + t * O_STRIDE, tmem_u + pcol + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)), idesc_pv,
                       (!first || ks > 0) ? 1u : 0u);
         if constexpr (F8) {
           if (two_term) {
 #pragma unroll
             for (int ks = 0; ks < TN / KEL; ++ks)
-              umma_ts<F8>(tmem_u + O_BASE + t * O_STRIDE, tmem_u + t * TN + 32 + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)),
+              umma_ts<F8>(tmem_u + O_BASE + t * O_STRIDE, tmem_u + pcol + 32 + ks * 8, vd + (uint64_t)(ks * ((KEL * 128) >> 4)),
                           idesc_pv, 1u);
           }
         }
@@ -672,6 +702,41 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
       if (!cur.valid || cur.uhi <= cur.ulo) continue;
       const int ulo = cur.ulo, uhi = cur.uhi;
       const int lo[2] = {cur.lo[0], cur.lo[1]}, hi[2] = {cur.hi[0], cur.hi[1]};
+      if constexpr (SDB) {
+        // one tile, two S buffers: QK runs a block ahead of PV (see SDB above).  Order QK(0) QK(1) | PV(i) QK(i+2).
+        wait(bar_q_full, qcnt & 1);
+        ++qcnt;
+        auto qk_next = [&](int j) {
+          const uint32_t ks = kr.slot, b = qkn & 1;
+          wait_tile(bar_k_full + 8 * ks, kr.phase);
+          issue_qk_to(0, ks, b ? S1_COL : 0u, bar_s_full + 8 * b);
+          ++qkn;
+          if (j + 1 == uhi) commit(bar_q_empty);     // the item's last QK: its Q slot may be refilled
+          commit(bar_k_empty + 8 * ks);
+          kr.advance();
+        };
+        qk_next(ulo);
+        if (ulo + 1 < uhi) qk_next(ulo + 1);
+        for (int i = ulo; i < uhi; ++i) {
+          const uint32_t b = pvn & 1, vs = vr.slot;
+          const bool first = i == ulo;
+          if (first) {   // O is overwritten: the previous item's epilogue must have read it
+            wait(bar_o_empty, (oecnt[0] & 1) ^ 1);
+            ++oecnt[0];
+          }
+          wait_tile(bar_v_full + 8 * vs, vr.phase);
+          wait(bar_p_full + 8 * b, (pvn >> 1) & 1);
+          tc_fence_after_sync();
+          issue_pv(0, vs, first, false, b ? S1_COL : 0u);
+          ++pvn;
+          commit(bar_pv_done);
+          commit(bar_v_empty + 8 * vs);
+          vr.advance();
+          if (i + 1 == uhi) commit(bar_o_full);
+          if (i + 2 < uhi) qk_next(i + 2);
+        }
+        continue;
+      }
       // prologue: QK of the first block
       {
         const uint32_t ks = kr.slot;
@@ -740,7 +805,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
     const int t = warp >> 2;                       // tile of this warpgroup
     const int r = (warp & 3) * 32 + lane;          // row within the tile == TMEM lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem + lane_base + t * TN;
+    const uint32_t tS0 = tmem + lane_base + t * TN;
     const uint32_t tO = tmem + lane_base + O_BASE + t * O_STRIDE;
     constexpr bool has_cap = CAP;
     uint32_t scnt = 0, ocnt = 0;
@@ -792,7 +857,10 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
       float m_used = -INFINITY, l = 0.f;
       float lr = 0.f;   // e4m3 only: sum of the ROUNDED probabilities (normalises O); l stays exact for the LSE
       for (int i = it.lo[t]; i < it.hi[t]; ++i) {
-        ok = wait_or_abort(bar_s_full + 8 * t, scnt & 1, s_abort);
+        // (one-tile kernels: S buffer and barrier pair alternate block by block, see SDB)
+        const uint32_t sb = SDB ? (scnt & 1) : (uint32_t)t;
+        const uint32_t tS = SDB ? tS0 + ((scnt & 1) ? S1_COL : 0u) : tS0;
+        ok = wait_or_abort(bar_s_full + 8 * sb, SDB ? ((scnt >> 1) & 1) : (scnt & 1), s_abort);
         ++scnt;
         if (!ok) { report_error(p.status, DEV_ERR_TIMEOUT, ROLE_SOFTMAX); break; }
         tc_fence_after_sync();
@@ -893,6 +961,12 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         }
         const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
         if (__any_sync(0xffffffffu, rescale)) {
+          if constexpr (SDB) {
+            // QK(i) was issued before PV(i-1): s_full no longer says that O is complete.  PV(i-1) is the PV number
+            // scnt - 2 of this CTA (scnt already counts this block); PV(i) cannot have been issued yet.
+            if (scnt >= 2 && !wait_or_abort(bar_pv_done, scnt & 1, s_abort)) ok = false;
+            tc_fence_after_sync();
+          }
           // O_t of the previous blocks is complete: the commit behind s_full also covered PV_t(i-1); PV_t(i)
           // cannot start before this thread's arrival below
 #pragma unroll 1
@@ -1005,7 +1079,7 @@ fwd_prefill_tc_kernel(const __grid_constant__ TcArgs a, const __grid_constant__ 
         tmem_wait_st();
         tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar_p_full + 8 * t);
+        if (lane == 0) mbar_arrive(bar_p_full + 8 * sb);
       }
       if (!ok) break;
       if (CAP && kCapEmuPairs > 0 && m_used == -INFINITY) l = 0.f;   // the cubic never returns exactly 0
