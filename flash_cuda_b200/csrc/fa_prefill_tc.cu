@@ -1491,8 +1491,8 @@ int launch_prefill_tc(const KParams& kp, const Plan& pl, int dtype, cudaStream_t
     return bf ? tc::launch_impl<__nv_bfloat16, 256, 256, 1, 1, 1>(kp, pl, dtype, kv_rows, stream)
               : tc::launch_impl<__half, 256, 256, 1, 1, 1>(kp, pl, dtype, kv_rows, stream);
   if (kp.hd == 192 && kp.hdv == 192)
-    return bf ? tc::launch_impl<__nv_bfloat16, 192, 192, 2, 1, 1>(kp, pl, dtype, kv_rows, stream)
-              : tc::launch_impl<__half, 192, 192, 2, 1, 1>(kp, pl, dtype, kv_rows, stream);
+    return bf ? tc::launch_impl<__nv_bfloat16, 192, 192, 1, 2, 1>(kp, pl, dtype, kv_rows, stream)
+              : tc::launch_impl<__half, 192, 192, 1, 2, 1>(kp, pl, dtype, kv_rows, stream);
   return -1;
 }
 
