@@ -378,7 +378,7 @@ def run_ours(args) -> None:
     dev = torch.device("cuda", local_rank)
     ops.load(build_if_missing=False)
     peaks = _peaks()
-    warm = max(args.warmup, 3)
+    warm = max(args.warmup, 10)      # untimed steps actually run before every timed region (reported as warmup_steps_run)
 
     # ---- headline: causal GQA prefill.  One SHARED problem of world x B sequences (the B-sequence batch of the
     # benchmark configuration repeated `world` times, identical on every rank); each rank computes its block of
