@@ -66,12 +66,27 @@ def _worker(rank, world, port, mode, ret):
                 cu_seqlens_q=p.cu_seqlens_q, max_seqlen_q=ql, max_seqlen_k_local=per,
                 softmax_scale=p.softmax_scale, causal=True, rank=rank, world=world, partial_fn=_oracle_partial,
                 combine_fn=_oracle_combine, s_aux=p.s_aux,
-                merge="all_to_all" if mode == "kv_a2a" else "all_gather")
+                merge={"kv_a2a": "all_to_all", "kv_auto": "auto"}.get(mode, "all_gather"))
             ref_out, ref_lse = ref_attention(p.q, p.k, p.v, **p.oracle_kw())
             ok = (out.float() - ref_out).abs().max().item() < 2e-2 and torch.allclose(lse, ref_lse, atol=1e-2)
         ret[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
+
+
+def test_merge_form_follows_the_rank_count():
+    assert MG.resolve_merge("auto", 2, 4096) == "all_gather"
+    assert MG.resolve_merge("auto", 4, 4096) == "all_to_all" and MG.resolve_merge("auto", 8, 4096) == "all_to_all"
+    assert MG.resolve_merge("auto", 4, 4097) == "all_gather"          # rows do not divide: one all-gather
+    assert MG.resolve_merge("all_gather", 8, 4096) == "all_gather"
+
+
+def test_four_rank_kv_sharding_with_the_automatic_merge():
+    world = 4
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), "kv_auto", ret), nprocs=world, join=True)
+    assert dict(ret) == {r: True for r in range(world)}
 
 
 @pytest.mark.parametrize("mode", ["heads", "kv", "kv_sink", "kv_a2a"])
