@@ -172,4 +172,76 @@ int launch_append_kv(const FaAppendParams& p, int num_sms, cudaStream_t stream) 
   return (int)cudaGetLastError();
 }
 
+// ------------------------------------------------------------------------------------------------------
+// De-paging: every sequence's K and V rows out of the page pool into contiguous slabs of `kpad` rows (slab b starts
+// at row b * kpad), 16 bytes per thread, a row's chunks on consecutive threads.  Rows from the sequence's end to
+// the end of its last 128-key block are written as zeros: the attention kernel loads whole blocks and gives those
+// rows weight zero, which needs finite values there.  Also writes the slabs' row offsets (batch + 1 words).
+struct DepageArgs {
+  const unsigned char* k;
+  const unsigned char* v;
+  unsigned char* k_out;
+  unsigned char* v_out;
+  const int32_t* page_table;
+  const int32_t* seqused_k;
+  int32_t* cu_out;
+  int64_t k_page_bytes, k_row_bytes, k_head_bytes, v_page_bytes, v_row_bytes, v_head_bytes;
+  int batch, kpad, hkv, page_shift, page_table_stride;
+  int k_hchunks, v_hchunks;      // 16-byte chunks per head of a K / V row
+};
+
+__global__ void __launch_bounds__(256) depage_kernel(const DepageArgs a) {
+  const int b = blockIdx.y;
+  if (blockIdx.x == 0 && b == 0 && threadIdx.x <= a.batch) a.cu_out[threadIdx.x] = threadIdx.x * a.kpad;
+  if (blockIdx.x == 0 && b == 0)
+    for (int i = threadIdx.x + 256; i <= a.batch; i += 256) a.cu_out[i] = i * a.kpad;
+  const int used = a.seqused_k[b];
+  const int rows = min((used + 127) / 128 * 128, a.kpad);
+  const int kc = a.hkv * a.k_hchunks, vc = a.hkv * a.v_hchunks, rc = kc + vc;     // chunks per (K row + V row)
+  const int64_t total = (int64_t)rows * rc;
+  const int32_t* pt = a.page_table + (int64_t)b * a.page_table_stride;
+  const int pmask = (1 << a.page_shift) - 1;
+  for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+    const int r = (int)(i / rc), c = (int)(i - (int64_t)r * rc);
+    const bool is_v = c >= kc;
+    const int cc = is_v ? c - kc : c;
+    const int hch = is_v ? a.v_hchunks : a.k_hchunks;
+    const int h = cc / hch, w = cc - h * hch;
+    int4 val = make_int4(0, 0, 0, 0);
+    if (r < used) {
+      const int pid = pt[r >> a.page_shift], slot = r & pmask;
+      const unsigned char* src = is_v ? a.v + pid * a.v_page_bytes + slot * a.v_row_bytes + h * a.v_head_bytes
+                                      : a.k + pid * a.k_page_bytes + slot * a.k_row_bytes + h * a.k_head_bytes;
+      val = *reinterpret_cast<const int4*>(src + (int64_t)w * 16);
+    }
+    unsigned char* dst = is_v ? a.v_out + ((int64_t)b * a.kpad + r) * ((int64_t)vc * 16)
+                              : a.k_out + ((int64_t)b * a.kpad + r) * ((int64_t)kc * 16);
+    *reinterpret_cast<int4*>(dst + (int64_t)cc * 16) = val;
+  }
+}
+
+int launch_depage(const KParams& kp, int kpad, void* k_out, void* v_out, int32_t* cu_out, int num_sms, cudaStream_t stream) {
+  const int esz = kp.kv_fp8 ? 1 : 2;
+  DepageArgs a;
+  a.k = reinterpret_cast<const unsigned char*>(kp.k);
+  a.v = reinterpret_cast<const unsigned char*>(kp.v);
+  a.k_out = reinterpret_cast<unsigned char*>(k_out);
+  a.v_out = reinterpret_cast<unsigned char*>(v_out);
+  a.page_table = kp.page_table;
+  a.seqused_k = kp.seqused_k;
+  a.cu_out = cu_out;
+  a.k_page_bytes = kp.k_page_stride * esz; a.k_row_bytes = kp.k_row_stride * esz; a.k_head_bytes = kp.k_head_stride * esz;
+  a.v_page_bytes = kp.v_page_stride * esz; a.v_row_bytes = kp.v_row_stride * esz; a.v_head_bytes = kp.v_head_stride * esz;
+  a.batch = kp.batch; a.kpad = kpad; a.hkv = kp.hkv; a.page_shift = kp.page_shift; a.page_table_stride = kp.page_table_stride;
+  a.k_hchunks = kp.hd * esz / 16; a.v_hchunks = kp.hdv * esz / 16;
+  if (kp.page_shift < 0 || kp.hd * esz % 16 || kp.hdv * esz % 16 || kp.batch <= 0) return (int)cudaErrorInvalidValue;
+  const int64_t per_seq = (int64_t)kpad * kp.hkv * (a.k_hchunks + a.v_hchunks);
+  int64_t bx = (per_seq + 256 * 8 - 1) / (256 * 8);        // about eight chunks per thread
+  const int64_t cap = (int64_t)num_sms * 16 / kp.batch + 1;
+  if (bx > cap) bx = cap;
+  if (bx < 1) bx = 1;
+  depage_kernel<<<dim3((unsigned)bx, (unsigned)kp.batch), 256, 0, stream>>>(a);
+  return (int)cudaGetLastError();
+}
+
 }  // namespace fa

@@ -17,6 +17,7 @@ int launch_sched(const FaSchedParams& sp, const Plan& pl, int32_t* out_dev, int3
                  int row_class = 0, int class_rows = 0);
 int launch_selftest_timeout(DeviceStatus* status, long long max_cycles, cudaStream_t stream);
 int launch_append_kv(const FaAppendParams& p, int num_sms, cudaStream_t stream);
+int launch_depage(const KParams& kp, int kpad, void* k_out, void* v_out, int32_t* cu_out, int num_sms, cudaStream_t stream);
 int launch_combine_strided(const float* o_part, const float* lse_part, int64_t o_split_stride, int64_t lse_split_stride,
                            int nsplits, int total_q, int hq, int hdv, const float* s_aux, void* out,
                            int64_t o_row_stride, int64_t o_head_stride, int out_dtype, float* lse, cudaStream_t stream);
@@ -180,9 +181,34 @@ static Plan decode_part_plan(const PlanInput& in, const Plan& pl) {
   return d;
 }
 
+// De-paging.  A prefill over pages of 1 .. 16 keys pays for its small copies in every query tile that reads a key
+// block (the tensor-core kernel runs at 500 - 900 TFLOP/s there against ~1150 over contiguous keys).  Where the keys
+// are read often enough - ceil(max_seqlen_q / 256) x (q heads per kv head) tiles per block, at least 4 - and the
+// batch's keys fit a bounded scratch, one pass copies every sequence's K and V rows out of the pages into contiguous
+// slabs of `kpad` rows in the workspace and the kernel runs on those with its contiguous-K/V producer (the
+// reference's route for page sizes its paged kernel has no producer for, kernels/fa4_blackwell.cu:9352-9378,
+// 9638-9679).  Decided from host-side facts only.
+constexpr size_t kDepageMaxBytes = (size_t)256 << 20;
+static bool depage_plan(const FaFwdParams* p, const Plan& pl, int* kpad, size_t* k_bytes, size_t* v_bytes) {
+  if (pl.route != FA_ROUTE_PREFILL_TC || !p->page_table) return false;
+  const int ps = p->page_size;
+  if (!(ps == 1 || ps == 2 || ps == 4 || ps == 8 || ps == 16)) return false;
+  if ((long long)ceil_div(p->max_seqlen_q, 256) * (p->hq / p->hkv) < 4) return false;
+  const size_t esz = p->kv_dtype == FA_DT_FP8_E4M3 ? 1 : 2;
+  const size_t rows = (size_t)p->batch * (size_t)((p->max_seqlen_k + 127) / 128 * 128);
+  const size_t kb = rows * p->hkv * p->hd * esz, vb = rows * p->hkv * p->hdv * esz;
+  if (kb + vb > kDepageMaxBytes) return false;
+  *kpad = (p->max_seqlen_k + 127) / 128 * 128;
+  *k_bytes = align_up(kb, 256);
+  *v_bytes = align_up(vb, 256);
+  return true;
+}
+
 // ---- workspace layout ----
 struct WsLayout {
   size_t header;      // DeviceStatus @0, counters @64
+  size_t dp_cu_off, dp_k_off, dp_v_off, dp_k_bytes;   // de-paged K/V slabs and their row offsets (dp_k_bytes 0: none)
+  int dp_kpad;
   size_t work_off, work_bytes;
   size_t work2_off, work2_bytes;   // mixed batches: the prefill kernel's list
   size_t lse_off, lse_bytes;
@@ -207,6 +233,20 @@ static WsLayout ws_layout(const FaFwdParams* p, const Plan& pl) {
       w.work2_off = off;
       w.work2_bytes = align_up((size_t)sched_len(pl, p->batch) * 4, 256);
       off += w.work2_bytes;
+    }
+  }
+  if (w.work2_bytes == 0) {
+    size_t kb = 0, vb = 0;
+    int kpad = 0;
+    if (depage_plan(p, pl, &kpad, &kb, &vb)) {
+      w.dp_kpad = kpad;
+      w.dp_cu_off = off;
+      off += align_up((size_t)(p->batch + 1) * 4, 256);
+      w.dp_k_off = off;
+      w.dp_k_bytes = kb;
+      off += kb;
+      w.dp_v_off = off;
+      off += vb;
     }
   }
   if (pl.nsplits > 1) {
@@ -418,6 +458,20 @@ int fa_b200_fwd(const FaFwdParams* p_in, void* workspace, size_t workspace_bytes
     rc = note_cuda_error(launch_prefill_tc(kp, pl, compute_dtype, stream), "tcgen05 prefill kernel");
   } else if (pl.route == FA_ROUTE_PREFILL_TC) {
     kp.work = p->scheduler_metadata;   // optional: the sorted (batch, tile) list replaces the arithmetic order
+    if (w.dp_k_bytes > 0) {
+      // small pages, keys read many times: copy them out of the pages once, then run over contiguous K/V
+      void* ks = ws + w.dp_k_off;
+      void* vs = ws + w.dp_v_off;
+      int32_t* cu = (int32_t*)(ws + w.dp_cu_off);
+      rc = note_cuda_error(launch_depage(kp, w.dp_kpad, ks, vs, cu, pl.num_sms, stream), "de-paging kernel");
+      if (rc != FA_OK) return rc;
+      kp.k = ks; kp.v = vs;
+      kp.k_row_stride = (int64_t)p->hkv * p->hd; kp.k_head_stride = p->hd; kp.k_page_stride = 0;
+      kp.v_row_stride = (int64_t)p->hkv * p->hdv; kp.v_head_stride = p->hdv; kp.v_page_stride = 0;
+      kp.page_table = nullptr; kp.page_size = 0; kp.page_shift = -1; kp.page_table_stride = 0; kp.num_pages = 0;
+      kp.cu_k = cu;                              // slab b starts at row b * kpad; lengths still come from seqused_k
+      kp.total_k = p->batch * w.dp_kpad;
+    }
     rc = note_cuda_error(launch_prefill_tc(kp, pl, compute_dtype, stream), "tcgen05 prefill kernel");
   } else {
     rc = note_cuda_error(launch_general(kp, compute_dtype, p->out_dtype, pl.num_sms, stream), "general kernel");

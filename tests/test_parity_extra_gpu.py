@@ -122,6 +122,24 @@ def test_e4m3_cache_decode_stage_starting_inside_a_page(page_size, cuda_device):
     _check(q, cuda_device, DEC, 6e-2, num_splits=5)
 
 
+@pytest.mark.parametrize("dtype", ["bf16", "fp8"])
+@pytest.mark.parametrize("page_size", [1, 4, 16])
+def test_prefill_over_small_pages_read_many_times_is_de_paged(page_size, dtype, cuda_device):
+    """Long query chunks over pages of 1 .. 16 keys: every key block is read by many query tiles, so the call copies
+    the sequences' keys out of the pages once and runs over contiguous K/V.  Ragged lengths (the slabs' tails are
+    zero-filled up to the next 128 keys), leftpad, a permuted page table, sink; with and without metadata."""
+    p = W.make_problem(f"depage_{page_size}_{dtype}", [(700, 700), (300, 901), (513, 640)], hq=8, hkv=2, hd=128,
+                       dtype=dtype, causal=True, page_size=page_size, leftpad=[0, 77, 0], sink=True, seed=62,
+                       fp8_scales="tensor" if dtype == "fp8" else "per_head")
+    tol = 6e-2 if dtype == "fp8" else 2e-2
+    _check(p, cuda_device, AUTO, tol)
+    _check(p, cuda_device, TC, tol, scheduler_metadata=_metadata_for(p, cuda_device))
+    w = W.make_problem(f"depage_win_{page_size}_{dtype}", [(1100, 1500)], hq=4, hkv=1, hd=128, dtype=dtype, causal=True,
+                       window_left=300, window_right=0, page_size=page_size, seed=63,
+                       fp8_scales="tensor" if dtype == "fp8" else "per_head")
+    _check(w, cuda_device, TC, tol)
+
+
 @pytest.mark.parametrize("hd,hdv", [(64, 64), (192, 128)])
 @pytest.mark.parametrize("page_size", [1, 4])
 def test_decode_route_small_pages_other_head_dims(page_size, hd, hdv, cuda_device):
